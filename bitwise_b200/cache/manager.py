@@ -79,9 +79,11 @@ class PagePool:
 
 @dataclass(frozen=True)
 class GroupSpec:
-    """Layers whose caches live and die together: ``window`` None keeps every key."""
+    """Layers whose caches live and die together: ``window`` None keeps every key; ``keep_first``: with a
+    window, the pages that hold a request's first ``keep_first`` keys are never given back."""
     window: Optional[int]
     entries: tuple  # cache entries (layer runs) of this group
+    keep_first: int = 0
 
 
 class RequestCache:
@@ -180,6 +182,10 @@ class CacheManager:
         self._h = self._lib.bw_cm_create(n, windows, pages, page_size, num_slots)
         if not self._h:
             _raise()
+        for g, spec in enumerate(self.groups):
+            if spec.window is not None and getattr(spec, "keep_first", 0):
+                if self._lib.bw_cm_set_keep(self._h, g, int(spec.keep_first)) < 0:
+                    _raise()
         self.pools = [_PoolView(self, g, int(pages_per_group[g])) for g in range(n)]
         self._info_buf = (ctypes.c_int * (3 + 2 * max(n, 1)))()
         self._need_buf = (ctypes.c_int * max(n, 1))()
@@ -350,11 +356,13 @@ class CacheManager:
 
 def groups_from_needs(needs: Sequence[object]) -> List[GroupSpec]:
     """Group cache entries by what must be kept: entries with paged keys and the same
-    window share a group (and so a block table); entries without paged keys form none."""
+    window (and the same number of first keys kept beside it) share a group (and so a block table);
+    entries without paged keys form none."""
     from ..parts.base import PagedKVNeed, PagedLatentNeed
-    by_window: Dict[Optional[int], List[int]] = {}
+    by_window: Dict[tuple, List[int]] = {}
     for e, need in enumerate(needs):
         if isinstance(need, (PagedKVNeed, PagedLatentNeed)):
-            by_window.setdefault(need.window, []).append(e)
-    keys = sorted(by_window, key=lambda w: (w is not None, w or 0))
-    return [GroupSpec(w, tuple(by_window[w])) for w in keys]
+            keep = int(getattr(need, "keep_first", 0) or 0) if need.window is not None else 0
+            by_window.setdefault((need.window, keep), []).append(e)
+    keys = sorted(by_window, key=lambda w: (w[0] is not None, w[0] or 0, w[1]))
+    return [GroupSpec(w, tuple(by_window[(w, k)]), k) for w, k in keys]

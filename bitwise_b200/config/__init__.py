@@ -2,10 +2,11 @@ from .base import ConfigError, read_config_json
 from .favudra import FavudraConfig, FavudraLayerConfig, FavudraMixerConfig
 from .llama import LlamaConfig, RopeScaling
 from .nuderax import LatentMixerConfig, NuderaxConfig, NuderaxLayerConfig, RoutedMlpConfig
+from .sebavik import BigramConfig, SebavikConfig, SebavikLayerConfig, SebavikMixerConfig, SebavikMlpConfig
 from .registry import (Architecture, architecture_of, config_from_folder, known_architectures,
                        lookup_architecture, register_architecture)
 
-__all__ = ["ConfigError", "FavudraConfig", "FavudraLayerConfig", "FavudraMixerConfig", "LlamaConfig", "RopeScaling", "NuderaxConfig", "NuderaxLayerConfig", "LatentMixerConfig",
+__all__ = ["BigramConfig", "SebavikConfig", "SebavikLayerConfig", "SebavikMixerConfig", "SebavikMlpConfig", "ConfigError", "FavudraConfig", "FavudraLayerConfig", "FavudraMixerConfig", "LlamaConfig", "RopeScaling", "NuderaxConfig", "NuderaxLayerConfig", "LatentMixerConfig",
            "RoutedMlpConfig", "read_config_json", "Architecture",
            "architecture_of", "config_from_folder", "known_architectures", "lookup_architecture",
            "register_architecture"]

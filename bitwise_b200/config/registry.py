@@ -67,3 +67,5 @@ def _ensure_builtin() -> None:
         from ..models import nuderax  # noqa: F401
     if "Favudra" not in _ARCHITECTURES:
         from ..models import favudra  # noqa: F401
+    if "Sebavik" not in _ARCHITECTURES:
+        from ..models import sebavik  # noqa: F401

@@ -79,6 +79,7 @@ struct RequestCache {
 
 struct CacheManager {
   std::vector<int> windows;  // per group: -1 keeps every key
+  std::vector<int> keep_blocks;  // per group: the first blocks of a request that a window never gives back
   int page_size;
   std::vector<PagePool> pools;
   int num_slots;
@@ -89,6 +90,7 @@ struct CacheManager {
   CacheManager(int groups, const int* win, const int* pages, int page, int slots) : page_size(page), num_slots(slots) {
     for (int g = 0; g < groups; ++g) {
       windows.push_back(win[g]);
+      keep_blocks.push_back(0);
       pools.emplace_back(pages[g]);
     }
     for (int s = slots - 1; s >= 0; --s) free_slots.push_back(s);
@@ -143,6 +145,7 @@ struct CacheManager {
       const int first_needed = length - windows[g] + 1;
       std::vector<int>& table = rc->tables[g];
       int& fl = rc->first_live[g];
+      if (fl < keep_blocks[g]) fl = keep_blocks[g];  // blocks that hold kept first keys stay with the request
       while (fl < static_cast<int>(table.size()) && (fl + 1) * page_size <= first_needed) {
         pools[g].release(table[fl]);
         table[fl] = kFreed;
@@ -384,6 +387,14 @@ BW_HOST_API int bw_pool_refcount(void* h, int page) {
 }
 
 // ---- cache manager -------------------------------------------------------------------------
+// A window group keeps the blocks that hold a request's first `tokens` keys for as long as it lives.
+BW_HOST_API int bw_cm_set_keep(void* h, int group, int tokens) {
+  CacheManager* m = static_cast<CacheManager*>(h);
+  if (group < 0 || group >= static_cast<int>(m->keep_blocks.size()) || tokens < 0) return fail("no group %d", group);
+  m->keep_blocks[group] = (tokens + m->page_size - 1) / m->page_size;
+  return 0;
+}
+
 BW_HOST_API void* bw_cm_create(int groups, const int* windows, const int* pages_per_group, int page_size, int num_slots) {
   if (page_size <= 0) {
     fail("page size must be positive");

@@ -4,7 +4,8 @@
 //    sigmoid(z); a correction per expert is added for the choice only; the experts form equal
 //    groups of neighbours, a group counts as the sum of its two largest choice scores, and only
 //    the experts of the best groups can be chosen; the weights are the chosen experts' scores
-//    times a constant.
+//    times a constant. `softmax_top`: the choice is by the logits themselves (plus the correction), and
+//    the weights are the softmax over the chosen logits only.
 //  * group_rows: (row, choice) pairs listed expert by expert, with the tiles of the grouped
 //    product that follows.
 //  * grouped_linear: out[i] = x[source(i)] W_g^T for the list entries i of every group g, W
@@ -28,7 +29,8 @@ namespace {
 // scores c[E] (-inf for the experts of groups that do not stay), group scores [groups].
 __global__ void __launch_bounds__(128)
 route_kernel(const float* __restrict__ z, const float* __restrict__ correction, int n, int experts, int groups,
-             int keep, int top, float weight_scale, int* __restrict__ chosen, float* __restrict__ weights) {
+             int keep, int top, float weight_scale, int softmax_top, int* __restrict__ chosen,
+             float* __restrict__ weights) {
   bw::pdl_enter();
   extern __shared__ float sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -39,9 +41,9 @@ route_kernel(const float* __restrict__ z, const float* __restrict__ correction, 
   float* gs = c + experts;
   const float* zr = z + static_cast<size_t>(r) * experts;
   for (int e = lane; e < experts; e += 32) {
-    const float v = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-zr[e])));
-    s[e] = v;
-    c[e] = __fadd_rn(v, correction ? correction[e] : 0.0f);
+    const float v = softmax_top ? zr[e] : __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-zr[e])));
+    s[e] = softmax_top ? 0.0f : v;  // (only its sign is used then: negative once taken)
+    c[e] = correction ? __fadd_rn(v, correction[e]) : v;
   }
   __syncwarp();
   const int per = experts / groups;
@@ -91,10 +93,23 @@ route_kernel(const float* __restrict__ z, const float* __restrict__ correction, 
     }
     if (lane == 0) {
       chosen[static_cast<size_t>(r) * top + k] = at;
-      weights[static_cast<size_t>(r) * top + k] = __fmul_rn(s[at], weight_scale);
+      weights[static_cast<size_t>(r) * top + k] = softmax_top ? zr[at] : __fmul_rn(s[at], weight_scale);
       s[at] = -1.0f;  // taken
     }
     __syncwarp();
+  }
+  if (softmax_top && lane == 0) {
+    // the softmax over the chosen logits, in the order of choice (the first is the largest)
+    float* wr = weights + static_cast<size_t>(r) * top;
+    float m = wr[0];
+    for (int k = 1; k < top; ++k) m = fmaxf(m, wr[k]);
+    float sum = 0.0f;
+    for (int k = 0; k < top; ++k) {
+      const float e = expf(__fsub_rn(wr[k], m));
+      wr[k] = e;
+      sum = __fadd_rn(sum, e);
+    }
+    for (int k = 0; k < top; ++k) wr[k] = __fmul_rn(__fdiv_rn(wr[k], sum), weight_scale);
   }
 }
 
@@ -462,11 +477,12 @@ __global__ void glu_clamped_kernel(const act_t* __restrict__ gate_up, act_t* __r
   }
 }
 
-// x[r] += d[r] + sum_j weights[r][j] * y[place[r * top + j]]; d may be null. VEC: four columns per
-// thread (the width a multiple of 4).
+// x[r] += d[r] + sum_j weights[r][j] * y[place[r * top + j]]; d may be null. With `scale` (one factor per
+// column) what is added is multiplied by it first. VEC: four columns per thread (the width a multiple of 4).
 template <bool VEC>
 __global__ void combine_kernel(float* x, const float* __restrict__ d, const float* __restrict__ y,
-                               const int* __restrict__ place, const float* __restrict__ weights, int top, int width) {
+                               const int* __restrict__ place, const float* __restrict__ weights, int top, int width,
+                               const float* __restrict__ scale) {
   bw::pdl_enter();
   constexpr int per = VEC ? 4 : 1;
   const int r = blockIdx.x;
@@ -490,14 +506,14 @@ __global__ void combine_kernel(float* x, const float* __restrict__ d, const floa
   for (int e = 0; e < per; ++e) {
     float v = s[e];
     if (d) v = __fadd_rn(d[o + e], v);
-    x[o + e] = __fadd_rn(x[o + e], v);
+    x[o + e] = scale ? __fmaf_rn(scale[c + e], v, x[o + e]) : __fadd_rn(x[o + e], v);
   }
 }
 
 }  // namespace
 
 BW_API int BW_FN(route)(const float* z, const float* correction, int n, int experts, int groups, int keep, int top,
-                        float weight_scale, int* chosen, float* weights, cudaStream_t stream) {
+                        float weight_scale, int softmax_top, int* chosen, float* weights, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (experts <= 0 || groups <= 0 || experts % groups || keep <= 0 || keep > groups || top <= 0 ||
       top > keep * (experts / groups)) {
@@ -511,7 +527,7 @@ BW_API int BW_FN(route)(const float* z, const float* correction, int n, int expe
     return -1;
   }
   bw::launch_pdl(route_kernel, dim3((n + warps - 1) / warps), dim3(warps * 32), smem, stream, z, correction, n, experts,
-                 groups, keep, top, weight_scale, chosen, weights);
+                 groups, keep, top, weight_scale, softmax_top, chosen, weights);
   return bw::launch_status();
 }
 
@@ -621,13 +637,13 @@ BW_API int BW_FN(glu_clamped)(const act_t* gate_up, act_t* out, int n, int inter
 }
 
 BW_API int BW_FN(combine)(float* x, const float* d, const float* y, const int* place, const float* weights, int n,
-                          int top, int width, cudaStream_t stream) {
+                          int top, int width, const float* scale, cudaStream_t stream) {
   if (n <= 0 || width <= 0) return 0;
   if (width % 4 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0)
     bw::launch_pdl(combine_kernel<true>, dim3(n, (width / 4 + 127) / 128), dim3(128), 0, stream, x, d, y, place, weights, top,
-                   width);
+                   width, scale);
   else
     bw::launch_pdl(combine_kernel<false>, dim3(n, (width + 255) / 256), dim3(256), 0, stream, x, d, y, place, weights, top,
-                   width);
+                   width, scale);
   return bw::launch_status();
 }

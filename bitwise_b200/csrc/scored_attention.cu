@@ -30,6 +30,10 @@ constexpr int kPrepWarps = 4;
 struct PrepArgs {
   const float* u;            // [n, cols] projected rows: q heads, then k heads, then v heads
   int cols;
+  const float* bias;         // [cols] added to every projected row (also to rows read from the state), or null
+  const float* vmix_src;     // [n, v_heads * vdim] values that this layer's values are mixed with, or null
+  const float* vmix_lambda;  // one number: v <- (1 - lambda) v + lambda vmix_src
+  float* v_keep;             // [n, v_heads * vdim]: the values as stored, kept in float32 for later layers, or null
   const float* conv_w;       // [cols, taps] or null
   const float* conv_wt;      // the same transposed, [taps, cols], for the kernel that reads four channels at a time
   int taps;
@@ -88,13 +92,23 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qkv_prepare_kernel(const Prep
             const int back = a.taps - 1 - t;
             if (p - back < 0) continue;
             const int rr = r - back;
-            const float src = rr >= row0
-                                  ? a.u[static_cast<size_t>(rr) * a.cols + c]
-                                  : a.conv_state[(static_cast<size_t>(slot) * (a.taps - 1) + (a.taps - 1 - (row0 - rr))) * a.cols + c];
+            float src = rr >= row0
+                            ? a.u[static_cast<size_t>(rr) * a.cols + c]
+                            : a.conv_state[(static_cast<size_t>(slot) * (a.taps - 1) + (a.taps - 1 - (row0 - rr))) * a.cols + c];
+            if (a.bias) src = __fadd_rn(src, a.bias[c]);
             v = __fmaf_rn(a.conv_w[static_cast<size_t>(c) * a.taps + t], src, v);
           }
         } else {
           v = a.u[static_cast<size_t>(r) * a.cols + c];
+          if (a.bias) v = __fadd_rn(v, a.bias[c]);
+        }
+        if (!turns && (a.vmix_src || a.v_keep)) {  // a value head (keys and queries turn or are normed; values neither)
+          const size_t at = static_cast<size_t>(r) * a.v_heads * a.vdim + (hs - a.heads - a.kv_heads) * a.vdim + e;
+          if (a.vmix_src) {
+            const float lam = a.vmix_lambda[0];
+            v = __fmaf_rn(lam, a.vmix_src[at], __fmul_rn(__fsub_rn(1.0f, lam), v));
+          }
+          if (a.v_keep) a.v_keep[at] = v;
         }
         ss = __fmaf_rn(v, v, ss);
       }
@@ -188,12 +202,30 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qkv_prepare_vec_kernel(const 
             const int rr = r - back;
             const float* src = rr >= row0 ? urow - static_cast<size_t>(back) * a.cols + c
                                           : a.conv_state + (static_cast<size_t>(slot) * (a.taps - 1) + (a.taps - 1 - (row0 - rr))) * a.cols + c;
-            const float4 x = *reinterpret_cast<const float4*>(src);
+            float4 x = *reinterpret_cast<const float4*>(src);
+            if (a.bias) {
+              const float4 b = *reinterpret_cast<const float4*>(a.bias + c);
+              x.x = __fadd_rn(x.x, b.x), x.y = __fadd_rn(x.y, b.y), x.z = __fadd_rn(x.z, b.z), x.w = __fadd_rn(x.w, b.w);
+            }
             const float4 w = *reinterpret_cast<const float4*>(a.conv_wt + static_cast<size_t>(t) * a.cols + c);
             v.x = __fmaf_rn(w.x, x.x, v.x), v.y = __fmaf_rn(w.y, x.y, v.y), v.z = __fmaf_rn(w.z, x.z, v.z), v.w = __fmaf_rn(w.w, x.w, v.w);
           }
         } else {
           v = *reinterpret_cast<const float4*>(urow + c);
+          if (a.bias) {
+            const float4 b = *reinterpret_cast<const float4*>(a.bias + c);
+            v.x = __fadd_rn(v.x, b.x), v.y = __fadd_rn(v.y, b.y), v.z = __fadd_rn(v.z, b.z), v.w = __fadd_rn(v.w, b.w);
+          }
+        }
+        if (!turns && (a.vmix_src || a.v_keep)) {  // a value head
+          const size_t at = static_cast<size_t>(r) * a.v_heads * a.vdim + (hs - a.heads - a.kv_heads) * a.vdim + e0;
+          if (a.vmix_src) {
+            const float lam = a.vmix_lambda[0], rest = __fsub_rn(1.0f, lam);
+            const float4 f = *reinterpret_cast<const float4*>(a.vmix_src + at);
+            v.x = __fmaf_rn(lam, f.x, __fmul_rn(rest, v.x)), v.y = __fmaf_rn(lam, f.y, __fmul_rn(rest, v.y));
+            v.z = __fmaf_rn(lam, f.z, __fmul_rn(rest, v.z)), v.w = __fmaf_rn(lam, f.w, __fmul_rn(rest, v.w));
+          }
+          if (a.v_keep) *reinterpret_cast<float4*>(a.v_keep + at) = v;
         }
         ss = __fmaf_rn(v.x, v.x, ss), ss = __fmaf_rn(v.y, v.y, ss), ss = __fmaf_rn(v.z, v.z, ss), ss = __fmaf_rn(v.w, v.w, ss);
       }
@@ -299,13 +331,33 @@ struct ScoreArgs {
   int sink;
   const float* slopes;  // [heads] or null
   int window;
+  const float* dist_a;  // [heads] or null: s <- s - dist_a[h] * ln(1 + dist_b[h] * (i - j))
+  const float* dist_b;
+  const float* sinks;   // [heads] or null: with `sink`, exp(sinks[h]) joins the denominator instead of exp(0)
+  int keep_first;       // with a window: the keys j < keep_first stay visible to every later position
 };
+
+// What a query's head takes off a score by distance.
+struct HeadBias {
+  float slope, a, b;
+};
+__device__ __forceinline__ HeadBias head_bias(const ScoreArgs& sa, int h, bool ok) {
+  HeadBias hb;
+  hb.slope = sa.slopes && ok ? sa.slopes[h] : 0.0f;
+  hb.a = sa.dist_a && ok ? sa.dist_a[h] : 0.0f;
+  hb.b = sa.dist_a && ok ? sa.dist_b[h] : 0.0f;
+  return hb;
+}
+// The first key a query at position pq sees inside its window (keys before keep_first are seen besides).
+__device__ __forceinline__ bool key_seen(const ScoreArgs& sa, int pq, int lo, int kp) {
+  return kp <= pq && (kp >= lo || kp < sa.keep_first);
+}
 
 #if BW_ACT_BF16
 // The same on the serving precision's tensor-core path, where the scores come from bfloat16
 // operands: tanh through the hardware's exponential, tanh(x) = 1 - 2 / (exp(2x) + 1) (relative
 // error of a few 1e-7, against the 4e-3 of a bfloat16 operand).
-__device__ __forceinline__ float modify_score_fast(float s, const ScoreArgs& sa, float slope, int pq, int kp) {
+__device__ __forceinline__ float modify_score_fast(float s, const ScoreArgs& sa, const HeadBias& hb, int pq, int kp) {
   if (sa.softcap > 0.0f) {
     // cap * tanh(x) = cap - 2 cap / (exp(2x) + 1), x = s * scale / cap; exp(2x) = 2^(s * cap_exp)
     const float e = bw::exp2_approx(__fmul_rn(s, sa.cap_exp));
@@ -313,16 +365,23 @@ __device__ __forceinline__ float modify_score_fast(float s, const ScoreArgs& sa,
   } else {
     s = __fmul_rn(s, sa.scale);
   }
-  if (sa.slopes) s = __fsub_rn(s, __fmul_rn(slope, static_cast<float>(pq - kp)));
+  if (sa.slopes) s = __fsub_rn(s, __fmul_rn(hb.slope, static_cast<float>(pq - kp)));
+  if (sa.dist_a) s = __fsub_rn(s, __fmul_rn(hb.a, __logf(__fmaf_rn(hb.b, static_cast<float>(pq - kp), 1.0f))));
   return s;
 }
 #endif
 
-__device__ __forceinline__ float modify_score(float s, const ScoreArgs& sa, float slope, int pq, int kp) {
+__device__ __forceinline__ float modify_score(float s, const ScoreArgs& sa, const HeadBias& hb, int pq, int kp) {
   s = __fmul_rn(s, sa.scale);
   if (sa.softcap > 0.0f) s = __fmul_rn(sa.softcap, tanhf(__fdiv_rn(s, sa.softcap)));
-  if (sa.slopes) s = __fsub_rn(s, __fmul_rn(slope, static_cast<float>(pq - kp)));
+  if (sa.slopes) s = __fsub_rn(s, __fmul_rn(hb.slope, static_cast<float>(pq - kp)));
+  if (sa.dist_a) s = __fsub_rn(s, __fmul_rn(hb.a, log1pf(__fmul_rn(hb.b, static_cast<float>(pq - kp)))));
   return s;
+}
+// Key tiles of `tile` keys that a walk from `from` visits: with kept first keys the tiles that hold
+// them, then the tiles from the window's first on; the tiles between are passed over.
+__device__ __forceinline__ int skip_gap(int k0, int keep_end, int win_begin) {
+  return (k0 >= keep_end && k0 < win_begin) ? win_begin : k0;
 }
 
 template <int ACC>
@@ -360,13 +419,15 @@ scored_attention_kernel(const act_t* __restrict__ q, int q_stride, const act_t* 
     for (int i = 0; i < ACC; ++i) acc[j][i] = 0.0f;
   }
   const int last = p0 + rows - 1;
-  const int first = sa.window > 0 ? max(0, p0 - sa.window + 1) : 0;  // pages before it may be gone
+  const int first = sa.window > 0 ? max(0, p0 - sa.window + 1) : 0;  // pages before it may be gone (kept first keys stay)
+  const int keep = sa.window > 0 ? sa.keep_first : 0;
+  const int keep_end = (keep + kKeys - 1) / kKeys * kKeys, win_begin = first / kKeys * kKeys;
   const int* bt = block_table + static_cast<size_t>(seq) * max_blocks;
-  for (int k0 = first / kKeys * kKeys; k0 <= last; k0 += kKeys) {
+  for (int k0 = skip_gap(0, keep_end, win_begin); k0 <= last; k0 = skip_gap(k0 + kKeys, keep_end, win_begin)) {
     __syncthreads();
     for (int kk = warp; kk < kKeys; kk += kWarps) {
       const int kp = k0 + kk;
-      const bool have = kp <= last && kp >= first;
+      const bool have = kp <= last && (kp >= first || kp < keep);
       size_t at = 0;
       if (have) at = (static_cast<size_t>(bt[kp / page]) * kv_heads + g) * page + kp % page;
       for (int d = lane; d < dim; d += 32) keys[kk * ks + d] = have ? bw::to_f(kcache[at * dim + d]) : 0.0f;
@@ -380,14 +441,14 @@ scored_attention_kernel(const act_t* __restrict__ q, int q_stride, const act_t* 
       if (qi >= nq) continue;
       const int pq = p0 + qi / nh;
       const int lo = sa.window > 0 ? max(0, pq - sa.window + 1) : 0;
-      if (k0 > pq || k0 + kKeys <= lo) continue;  // no key of the tile is seen: the state stays
+      if (k0 > pq || (k0 + kKeys <= lo && k0 >= keep)) continue;  // no key of the tile is seen: the state stays
       const int kp = k0 + lane;
       const float* qv = qs + qi * dim;
       const float* kv = keys + lane * ks;
       float s = 0.0f;
       for (int d = 0; d < dim; ++d) s = __fmaf_rn(qv[d], kv[d], s);
-      s = modify_score(s, sa, sa.slopes ? sa.slopes[h0 + qi % nh] : 0.0f, pq, kp);
-      const bool seen = kp <= pq && kp >= lo;
+      s = modify_score(s, sa, head_bias(sa, h0 + qi % nh, true), pq, kp);
+      const bool seen = key_seen(sa, pq, lo, kp);
       if (!seen) s = -INFINITY;
       const float mt = bw::warp_max(s);
       const float mn = fmaxf(m[j], mt);
@@ -414,7 +475,7 @@ scored_attention_kernel(const act_t* __restrict__ q, int q_stride, const act_t* 
     const int qi = warp + kWarps * j;
     if (qi >= nq) continue;
     float den = l[j];
-    if (sa.sink) den = __fadd_rn(den, expf(-m[j]));  // the extra key of score 0
+    if (sa.sink) den = __fadd_rn(den, expf(__fsub_rn(sa.sinks ? sa.sinks[h0 + qi % nh] : 0.0f, m[j])));  // the extra key (score 0 unless given)
     const float inv = __fdiv_rn(1.0f, den);
     act_t* dst = out + static_cast<size_t>(row0 + qi / nh) * o_stride + (h0 + qi % nh) * vdim;
 #pragma unroll
@@ -493,8 +554,8 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
   const bool ok_a = sr_a < nq, ok_b = sr_b < nq;
   const int pq_a = p0 + (ok_a ? sr_a / nh : 0), pq_b = p0 + (ok_b ? sr_b / nh : 0);
   const int lo_a = sa.window > 0 ? max(0, pq_a - sa.window + 1) : 0, lo_b = sa.window > 0 ? max(0, pq_b - sa.window + 1) : 0;
-  const float slope_a = sa.slopes && ok_a ? sa.slopes[h0 + sr_a % nh] : 0.0f;
-  const float slope_b = sa.slopes && ok_b ? sa.slopes[h0 + sr_b % nh] : 0.0f;
+  const HeadBias slope_a = head_bias(sa, h0 + sr_a % nh, ok_a), slope_b = head_bias(sa, h0 + sr_b % nh, ok_b);
+  const int keep = sa.window > 0 ? sa.keep_first : 0;
   // the positions that this warp's queries span: tiles outside are skipped by the whole warp
   const int w_first = min(warp * 16, max(nq - 1, 0)) / nh, w_last = min(warp * 16 + 15, max(nq - 1, 0)) / nh;
   const int w_lo = sa.window > 0 ? max(0, p0 + w_first - sa.window + 1) : 0, w_hi = p0 + w_last;
@@ -507,13 +568,14 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
 #pragma unroll
   for (int j = 0; j < VT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
   const int last = p0 + rows - 1;
-  const int first = sa.window > 0 ? max(0, p0 - sa.window + 1) : 0;  // pages before it may be gone
+  const int first = sa.window > 0 ? max(0, p0 - sa.window + 1) : 0;  // pages before it may be gone (kept first keys stay)
+  const int keep_end = (keep + kMmaKeys - 1) / kMmaKeys * kMmaKeys, win_begin = first / kMmaKeys * kMmaKeys;
   const int* bt = block_table + static_cast<size_t>(seq) * max_blocks;
   // With spans the block walks the key tiles span * span_tiles .. + span_tiles - 1 only (fixed
   // absolute positions again) and leaves a record for the merge instead of the result.
-  int k_begin = first / kMmaKeys * kMmaKeys, k_end = last;
+  int k_begin = skip_gap(0, keep_end, win_begin), k_end = last;
   if (span_tiles > 0) {
-    k_begin = max(k_begin, span * span_tiles * kMmaKeys);
+    k_begin = skip_gap(max(k_begin, span * span_tiles * kMmaKeys), keep_end, win_begin);
     k_end = min(k_end, (span + 1) * span_tiles * kMmaKeys - 1);
     if (k_begin > k_end) {
       // none of the block's queries reaches into this span: records that say so, nothing else
@@ -546,7 +608,7 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
     // a thread copies one 16-byte part of the keys kk0, kk0 + kstep, ...: its part and first key are fixed
     for (int kk = kk0_k; kk < kMmaKeys; kk += kstep_k) {
       const int kp = k0 + kk;
-      const bool have = kp <= last && kp >= first && part_k < dparts;
+      const bool have = kp <= last && (kp >= first || kp < keep) && part_k < dparts;
       const __nv_bfloat16* src = kcache;
       if (have) {
         const int blk = page_shift >= 0 ? kp >> page_shift : kp / page, slot = kp - blk * page;
@@ -557,7 +619,7 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
     if (vcache) {
       for (int kk = kk0_v; kk < kMmaKeys; kk += kstep_v) {
         const int kp = k0 + kk;
-        const bool have = kp <= last && kp >= first && part_v < vparts;
+        const bool have = kp <= last && (kp >= first || kp < keep) && part_v < vparts;
         const __nv_bfloat16* src = vcache;
         if (have) {
           const int blk = page_shift >= 0 ? kp >> page_shift : kp / page, slot = kp - blk * page;
@@ -569,11 +631,12 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
     bw::copies_commit();
   };
   if (k_begin <= k_end) request_tile(k_begin, 0);
-  for (int k0 = k_begin, buf = 0; k0 <= k_end; k0 += kMmaKeys, buf ^= 1) {
+  for (int k0 = k_begin, buf = 0; k0 <= k_end; k0 = skip_gap(k0 + kMmaKeys, keep_end, win_begin), buf ^= 1) {
     // the next tile is requested while this one is used; its buffer was released by the
     // barrier at the end of the step before
-    if (k0 + kMmaKeys <= k_end) {
-      request_tile(k0 + kMmaKeys, buf ^ 1);
+    const int k_next = skip_gap(k0 + kMmaKeys, keep_end, win_begin);
+    if (k_next <= k_end) {
+      request_tile(k_next, buf ^ 1);
       bw::copies_wait<1>();
     } else {
       bw::copies_wait<0>();
@@ -581,7 +644,7 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
     __syncthreads();
     const __nv_bfloat16* ks = ks_all + buf * kMmaKeys * kst;
     const __nv_bfloat16* vs = vs_all + buf * kMmaKeys * vst;
-    if (warp_has_rows && k0 <= w_hi && k0 + kMmaKeys > w_lo) {
+    if (warp_has_rows && k0 <= w_hi && (k0 + kMmaKeys > w_lo || k0 < keep)) {
     // scores of 16 queries x 32 keys
     float sc[4][4];
 #pragma unroll
@@ -598,7 +661,7 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
     }
     float mt_a = -INFINITY, mt_b = -INFINITY;
     // a tile that every query of the warp sees whole needs no mask
-    const bool whole = warp_full && k0 + kMmaKeys - 1 <= w_seen_to && k0 >= w_seen_from;
+    const bool whole = warp_full && k0 + kMmaKeys - 1 <= w_seen_to && (k0 >= w_seen_from || k0 + kMmaKeys <= keep);
     if (whole) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -619,8 +682,8 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
           const int kp = k0 + j * 8 + 2 * (lane & 3) + e;
           float va = modify_score_fast(sc[j][e], sa, slope_a, pq_a, kp);
           float vb = modify_score_fast(sc[j][2 + e], sa, slope_b, pq_b, kp);
-          if (!(ok_a && kp <= pq_a && kp >= lo_a)) va = -INFINITY;
-          if (!(ok_b && kp <= pq_b && kp >= lo_b)) vb = -INFINITY;
+          if (!(ok_a && key_seen(sa, pq_a, lo_a, kp))) va = -INFINITY;
+          if (!(ok_b && key_seen(sa, pq_b, lo_b, kp))) vb = -INFINITY;
           sc[j][e] = va, sc[j][2 + e] = vb;
           mt_a = fmaxf(mt_a, va), mt_b = fmaxf(mt_b, vb);
         }
@@ -696,7 +759,10 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
     }
     return;
   }
-  if (sa.sink) l_a = __fadd_rn(l_a, expf(-m_a)), l_b = __fadd_rn(l_b, expf(-m_b));  // the extra key of score 0
+  if (sa.sink) {  // the extra key (score 0 unless the head has a number of its own)
+    const float sk_a = sa.sinks && ok_a ? sa.sinks[h0 + sr_a % nh] : 0.0f, sk_b = sa.sinks && ok_b ? sa.sinks[h0 + sr_b % nh] : 0.0f;
+    l_a = __fadd_rn(l_a, expf(__fsub_rn(sk_a, m_a))), l_b = __fadd_rn(l_b, expf(__fsub_rn(sk_b, m_b)));
+  }
   const float inv_a = __fdiv_rn(1.0f, l_a), inv_b = __fdiv_rn(1.0f, l_b);
   const int col = 2 * (lane & 3);
   if (ok_a) {
@@ -716,7 +782,7 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
 // The spans' records of a query joined in ascending order of the spans: a warp per query.
 __global__ void __launch_bounds__(128)
 scored_attention_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* out, int o_stride, int queries, int heads,
-                              int vdim, int spans, int sink) {
+                              int vdim, int spans, int sink, const float* __restrict__ sinks) {
   bw::pdl_enter();
   const int qi = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (qi >= queries) return;
@@ -738,7 +804,7 @@ scored_attention_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* 
       if (d < vdim) acc[i] = __fmaf_rn(r[2 + d], f, acc[i]);
     }
   }
-  if (sink) l = __fadd_rn(l, expf(-m));
+  if (sink) l = __fadd_rn(l, expf(__fsub_rn(sinks ? sinks[qi % heads] : 0.0f, m)));
   const float inv = __fdiv_rn(1.0f, l);
   __nv_bfloat16* dst = out + static_cast<size_t>(qi / heads) * o_stride + (qi % heads) * vdim;
 #pragma unroll
@@ -788,6 +854,7 @@ BW_API int BW_FN(qkv_prepare)(const float* u, int cols, const float* conv_w, con
                               int pairs, const int* pos, const int* row_seq, const int* seq_row0, const int* seq_pos0,
                               const int* seq_slot, const int* block_table, int max_blocks, void* kcache, void* vcache,
                               void* q_out, int n, int heads, int kv_heads, int dim, int vdim, int page,
+                              const float* bias, const float* vmix_src, const float* vmix_lambda, float* v_keep,
                               cudaStream_t stream) {
   if (n <= 0) return 0;
   if (dim > kMaxE * 32 || vdim > kMaxE * 32) {
@@ -799,6 +866,7 @@ BW_API int BW_FN(qkv_prepare)(const float* u, int cols, const float* conv_w, con
     return -1;
   }
   PrepArgs a;
+  a.bias = bias, a.vmix_src = vmix_src, a.vmix_lambda = vmix_lambda, a.v_keep = v_keep;
   a.u = u, a.cols = cols, a.conv_w = conv_w, a.conv_wt = conv_w ? conv_wt : nullptr, a.taps = taps;
   a.conv_state = taps > 1 ? conv_state : nullptr;
   a.q_norm = q_norm, a.k_norm = k_norm, a.eps = eps, a.cos_t = cos_t, a.sin_t = sin_t, a.pairs = cos_t ? pairs : 0;
@@ -811,7 +879,8 @@ BW_API int BW_FN(qkv_prepare)(const float* u, int cols, const float* conv_w, con
   const bool by_four = dim % 4 == 0 && vdim % 4 == 0 && cols % 4 == 0 && (!conv_w || conv_wt) &&
                        ((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(conv_state) |
                          reinterpret_cast<uintptr_t>(conv_wt) | reinterpret_cast<uintptr_t>(q_norm) |
-                         reinterpret_cast<uintptr_t>(k_norm)) & 15) == 0;
+                         reinterpret_cast<uintptr_t>(k_norm) | reinterpret_cast<uintptr_t>(bias) |
+                         reinterpret_cast<uintptr_t>(vmix_src) | reinterpret_cast<uintptr_t>(v_keep)) & 15) == 0;
   if (by_four)
     bw::launch_pdl(qkv_prepare_vec_kernel, dim3(n, (total + kPrepWarps - 1) / kPrepWarps), dim3(kPrepWarps * 32), 0, stream, a);
   else
@@ -836,7 +905,8 @@ BW_API int BW_FN(scored_attention)(const void* q, int q_stride, const void* kcac
                                    const int* block_table, int max_blocks, const int* tile_seq, const int* tile_row0,
                                    const int* tile_rows, int tiles, const int* seq_pos0, const int* seq_row0, void* out,
                                    int o_stride, int heads, int kv_heads, int dim, int vdim, int page, float scale,
-                                   float softcap, int sink, const float* slopes, int window, cudaStream_t stream) {
+                                   float softcap, int sink, const float* slopes, int window, const float* dist_a,
+                                   const float* dist_b, const float* sinks, int keep_first, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (kv_heads <= 0 || heads % kv_heads) {
     bw::set_error("scored_attention: %d heads on %d key/value heads", heads, kv_heads);
@@ -857,6 +927,7 @@ BW_API int BW_FN(scored_attention)(const void* q, int q_stride, const void* kcac
   }
   ScoreArgs sa;
   sa.scale = scale, sa.softcap = softcap, sa.sink = sink, sa.slopes = slopes, sa.window = window;
+  sa.dist_a = dist_a, sa.dist_b = dist_a ? dist_b : nullptr, sa.sinks = sinks, sa.keep_first = window > 0 ? keep_first : 0;
   sa.cap_exp = 0.0f;  // (the tensor-core kernel's)
   const dim3 grid(tiles, kv_heads, (rep + hb - 1) / hb);
 #define BW_SCORED(A)                                                                                                      \
@@ -892,7 +963,8 @@ BW_API int bw_bf16_scored_attention_mma(const void* q, int q_stride, const void*
                                         const int* tile_rows, int tiles, const int* seq_pos0, const int* seq_row0, void* out,
                                         int o_stride, int heads, int kv_heads, int dim, int vdim, int page, float scale,
                                         float softcap, int sink, const float* slopes, int window, int n, int spans,
-                                        float* partial, cudaStream_t stream) {
+                                        float* partial, const float* dist_a, const float* dist_b, const float* sinks,
+                                        int keep_first, cudaStream_t stream) {
   // spans > 1 (`partial` holding n * heads * spans * (vdim + 2) floats): every query's keys are spread
   // over blocks of kSpanTiles key tiles each, at fixed absolute positions, and a second kernel joins
   // the spans' records in ascending order.
@@ -907,6 +979,7 @@ BW_API int bw_bf16_scored_attention_mma(const void* q, int q_stride, const void*
                        (vcache ? static_cast<size_t>(2 * kMmaKeys) * (vdim + 8) : 0)) * sizeof(__nv_bfloat16);
   ScoreArgs sa;
   sa.scale = scale, sa.softcap = softcap, sa.sink = sink, sa.slopes = slopes, sa.window = window;
+  sa.dist_a = dist_a, sa.dist_b = dist_a ? dist_b : nullptr, sa.sinks = sinks, sa.keep_first = window > 0 ? keep_first : 0;
   sa.cap_exp = softcap > 0.0f ? 2.0f * scale / softcap * 1.4426950408889634f : 0.0f;
   const bool split = spans > 1 && partial != nullptr;
   if (!split) spans = 1;
@@ -927,7 +1000,7 @@ BW_API int bw_bf16_scored_attention_mma(const void* q, int q_stride, const void*
 #undef BW_SCORED_MMA
   if (rc != 0 || !split) return rc;
   bw::launch_pdl(scored_attention_merge_kernel, dim3((n * heads + 3) / 4), dim3(128), 0, stream,
-                 static_cast<const float*>(partial), static_cast<__nv_bfloat16*>(out), o_stride, n * heads, heads, vdim, spans, sink);
+                 static_cast<const float*>(partial), static_cast<__nv_bfloat16*>(out), o_stride, n * heads, heads, vdim, spans, sink, sinks);
   return bw::launch_status();
 }
 

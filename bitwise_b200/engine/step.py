@@ -45,12 +45,13 @@ class OutOfPages(StepError):
 def query_tile_rows(model, ops=None) -> List[int]:
     """The distinct query-tile heights that the model's mixers ask for on the kernel library ``ops``."""
     sizes = set()
-    for b in model.blocks:
-        fn = getattr(b.mixer, "query_tile_rows", None)
+    users = [p for b in model.blocks for p in (b.mixer, b)] + [getattr(model, "embedding", None)]
+    for part in users:
+        fn = getattr(part, "query_tile_rows", None)
         if fn is not None:
             try:
                 got = fn(ops)
-            except TypeError:  # a mixer that takes no argument
+            except TypeError:  # a part that takes no argument
                 got = fn()
             sizes.update(int(v) for v in (got if isinstance(got, (list, tuple, set)) else [got]))
     return sorted(sizes) or [16]

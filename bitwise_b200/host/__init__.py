@@ -31,6 +31,7 @@ def lib():
         "bw_pool_fork": (c_int, [c_void_p, c_int]), "bw_pool_release": (c_int, [c_void_p, c_int]),
         "bw_pool_refcount": (c_int, [c_void_p, c_int]),
         "bw_cm_create": (c_void_p, [c_int, ip, ip, c_int, c_int]), "bw_cm_destroy": (None, [c_void_p]),
+        "bw_cm_set_keep": (c_int, [c_void_p, c_int, c_int]),
         "bw_cm_begin": (c_int, [c_void_p, c_int64]), "bw_cm_has": (c_int, [c_void_p, c_int64]),
         "bw_cm_ensure": (c_int, [c_void_p, c_int64, c_int]), "bw_cm_advance": (c_int, [c_void_p, c_int64, c_int]),
         "bw_cm_release": (c_int, [c_void_p, c_int64, c_int]), "bw_cm_fork": (c_int, [c_void_p, c_int64, c_int64]),

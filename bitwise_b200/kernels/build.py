@@ -43,6 +43,10 @@ KERNEL_SETS: Dict[str, List[tuple]] = {
                    ("linear_recurrence.cu", ["-DBW_ACT_BF16=0"])],
     "bf16_mixers": [("common.cu", []), ("sublayer_norm.cu", ["-DBW_ACT_BF16=1"]), ("scored_attention.cu", ["-DBW_ACT_BF16=1"]),
                     ("linear_recurrence.cu", ["-DBW_ACT_BF16=1"])],
+    # kernels on the residual stream for blocks with scaled residuals, a convolution on what the sublayers read,
+    # a per-layer token input and an average over the layers' results; the embedding with a second table
+    "f32_stream": [("common.cu", []), ("stream_ops.cu", ["-DBW_ACT_BF16=0"])],
+    "bf16_stream": [("common.cu", []), ("stream_ops.cu", ["-DBW_ACT_BF16=1"])],
 }
 
 # head sizes whose attention library a full build prepares (others are compiled when a model asks)
@@ -220,6 +224,7 @@ def ensure_host_built(verbose: bool = True) -> str:
 def build_all(verbose: bool = True) -> List[str]:
     """Compile every kernel set (what a 'does it build' check wants)."""
     out = [ensure_host_built(verbose)]
-    out += [ensure_built(k, (), verbose) for k in ("f32", "bf16", "f32_parts", "bf16_parts", "f32_mixers", "bf16_mixers")]
+    out += [ensure_built(k, (), verbose) for k in ("f32", "bf16", "f32_parts", "bf16_parts", "f32_mixers", "bf16_mixers",
+                                                         "f32_stream", "bf16_stream")]
     out += [ensure_built("bf16_attn", (f"BW_HEAD_DIM={hd}",), verbose) for hd in DEFAULT_HEAD_DIMS]
     return out

@@ -308,7 +308,7 @@ class KernelOps:
             dev = torch.device("cuda", self._device_index())
             self._failure_word = torch.zeros(1, dtype=torch.int32, device=dev)
             self._failure_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
-            for lib in [self.lib] + list(self._attn_libs.values()) + [l for l in [getattr(self, "_parts", None), getattr(self, "_mixers", None)] if l]:
+            for lib in [self.lib] + list(self._attn_libs.values()) + [l for l in [getattr(self, "_parts", None), getattr(self, "_mixers", None), getattr(self, "_streamlib", None)] if l]:
                 lib.bw_set_failure_word(_p(self._failure_word))
         return self._failure_word, self._failure_host
 
@@ -771,11 +771,13 @@ class KernelOps:
                     _c_int(page), _c_int(window), _c_float(scale), self._stream())
 
     def route(self, logits: torch.Tensor, correction: Optional[torch.Tensor], groups: int, keep: int, top: int,
-              weight_scale: float, chosen: torch.Tensor, weights: torch.Tensor) -> None:
+              weight_scale: float, chosen: torch.Tensor, weights: torch.Tensor, softmax_top: bool = False) -> None:
         """Per row of ``logits`` (float32 [n, experts]): scores sigmoid(z); the ``top`` experts with
         the largest score + correction among the experts of the ``keep`` best of ``groups`` equal
         groups of neighbours (a group counts as the sum of its two largest corrected scores);
-        chosen int32 [n, top], weights float32 [n, top] = score * weight_scale."""
+        chosen int32 [n, top], weights float32 [n, top] = score * weight_scale.  ``softmax_top``: the choice
+        is by the logits themselves (plus the correction) and the weights are the softmax over the chosen
+        logits only, times weight_scale."""
         n, experts = logits.shape
         _need(logits, torch.float32, "route logits", 2)
         _need(chosen, torch.int32, "route chosen", 2)
@@ -785,7 +787,8 @@ class KernelOps:
         if tuple(chosen.shape) != (n, top) or tuple(weights.shape) != (n, top):
             raise KernelError("route: outputs are not [rows, top]")
         self._pcall("route", _p(logits), _p(correction), _c_int(n), _c_int(experts), _c_int(groups), _c_int(keep),
-                    _c_int(top), _c_float(weight_scale), _p(chosen), _p(weights), self._stream())
+                    _c_int(top), _c_float(weight_scale), _c_int(int(bool(softmax_top))), _p(chosen), _p(weights),
+                    self._stream())
 
     def group_rows(self, chosen: torch.Tensor, experts: int, group_off: torch.Tensor, tile_prefix: torch.Tensor,
                    order: torch.Tensor, place: torch.Tensor) -> None:
@@ -874,8 +877,9 @@ class KernelOps:
                     self._stream())
 
     def combine(self, x: torch.Tensor, d: Optional[torch.Tensor], y: torch.Tensor, place: torch.Tensor,
-                weights: torch.Tensor, top: int) -> None:
-        """x[r] += d[r] + sum_j weights[r, j] * y[place[r * top + j]] (float32; d may be None)."""
+                weights: torch.Tensor, top: int, scale: Optional[torch.Tensor] = None) -> None:
+        """x[r] += d[r] + sum_j weights[r, j] * y[place[r * top + j]] (float32; d may be None); with ``scale``
+        [width] what is added is multiplied by it column by column first."""
         n, width = x.shape
         _need(x, torch.float32, "combine x", 2)
         _need(y, torch.float32, "combine y", 2)
@@ -885,8 +889,12 @@ class KernelOps:
             _need(d, torch.float32, "combine d", 2)
         if y.shape[1] != width or tuple(weights.shape) != (n, top) or (d is not None and d.shape != x.shape):
             raise KernelError("combine: shapes differ")
+        if scale is not None:
+            _need(scale, torch.float32, "combine scale", 1)
+            if scale.shape[0] != width:
+                raise KernelError("combine: one factor per column is needed")
         self._pcall("combine", _p(x), _p(d), _p(y), _p(place), _p(weights), _c_int(n), _c_int(top), _c_int(width),
-                    self._stream())
+                    _p(scale), self._stream())
 
     # -- mixers with state beside or instead of pages, and the norm after a sublayer (their library
     #    is loaded at first use) -------------------------------------------------------------------
@@ -965,7 +973,9 @@ class KernelOps:
                     q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
                     cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], batch, block_table: torch.Tensor,
                     kcache: torch.Tensor, vcache: Optional[torch.Tensor], q_out: torch.Tensor, heads: int,
-                    write_kv_heads: int, dim: int, vdim: int, conv_wt: Optional[torch.Tensor] = None) -> None:
+                    write_kv_heads: int, dim: int, vdim: int, conv_wt: Optional[torch.Tensor] = None,
+                    bias: Optional[torch.Tensor] = None, vmix_src: Optional[torch.Tensor] = None,
+                    vmix_lambda: Optional[torch.Tensor] = None, v_keep: Optional[torch.Tensor] = None) -> None:
         """From the projected rows ``u`` (float32 [n, cols]: ``heads`` query heads of ``dim``, then, when
         ``write_kv_heads`` > 0, that many key heads of ``dim`` and, with ``vcache``, value heads of
         ``vdim``): the convolution over time with ``conv_w`` [cols, taps] (inputs before the step's
@@ -974,7 +984,9 @@ class KernelOps:
         pairs entries of q and k by the tables' row of the position; q into ``q_out`` [n, heads * dim],
         keys and values into their pages.  Each step may be absent (None).  ``conv_wt``: the taps
         transposed ([taps, cols]); with them, and sizes that are multiples of 4, the kernel reads four
-        channels at a time."""
+        channels at a time.  ``bias`` [cols] is added to every projected row first.  ``vmix_src`` (float32 [n,
+        kv_heads * vdim]) and ``vmix_lambda`` (one float32): the values become (1 - lambda) v + lambda vmix_src
+        before they are stored; ``v_keep`` (same shape) receives the values as stored, in float32."""
         n, cols = u.shape
         _need(u, torch.float32, "qkv_prepare u", 2)
         _need(q_out, self.act_dtype, "qkv_prepare q_out", 2)
@@ -1005,6 +1017,19 @@ class KernelOps:
             _need(vcache, self.act_dtype, "qkv_prepare vcache", 4)
             if write_kv_heads and tuple(vcache.shape[1:]) != (write_kv_heads, kcache.shape[2], vdim):
                 raise KernelError("qkv_prepare: value cache is not [pages, kv_heads, page, vdim]")
+        if bias is not None:
+            _need(bias, torch.float32, "qkv_prepare bias", 1)
+            if bias.shape[0] != cols:
+                raise KernelError("qkv_prepare: one bias per projected column is needed")
+        for t_, what in ((vmix_src, "vmix_src"), (v_keep, "v_keep")):
+            if t_ is not None:
+                _need(t_, torch.float32, "qkv_prepare " + what, 2)
+                if vcache is None or not write_kv_heads or tuple(t_.shape) != (n, write_kv_heads * vdim):
+                    raise KernelError(f"qkv_prepare: {what} is not [rows, kv_heads * vdim] of values that are stored")
+        if (vmix_src is None) != (vmix_lambda is None):
+            raise KernelError("qkv_prepare: mixing values needs both the other values and the factor")
+        if vmix_lambda is not None:
+            _need(vmix_lambda, torch.float32, "qkv_prepare vmix_lambda", 1)
         if conv_wt is not None:
             _need(conv_wt, torch.float32, "qkv_prepare conv_wt", 2)
             if conv_w is None or tuple(conv_wt.shape) != (taps, cols):
@@ -1013,7 +1038,8 @@ class KernelOps:
                     _c_float(eps), _p(cos), _p(sin), _c_int(pairs), _p(batch.pos), _p(batch.row_seq), _p(batch.seq_row0),
                     _p(batch.seq_pos0), _p(batch.seq_slot), _p(block_table), _c_int(block_table.shape[1]), _p(kcache),
                     _p(vcache if write_kv_heads else None), _p(q_out), _c_int(n), _c_int(heads), _c_int(write_kv_heads),
-                    _c_int(dim), _c_int(vdim), _c_int(kcache.shape[2]), self._stream())
+                    _c_int(dim), _c_int(vdim), _c_int(kcache.shape[2]), _p(bias), _p(vmix_src), _p(vmix_lambda), _p(v_keep),
+                    self._stream())
 
     def conv_state_update(self, u: torch.Tensor, state: torch.Tensor, batch, taps: int, seq_tiles) -> None:
         """state[slot of s][i] = the projected row of position end_s - (taps - 1) + i for every sequence s
@@ -1030,11 +1056,15 @@ class KernelOps:
     def scored_attention(self, q: torch.Tensor, kcache: torch.Tensor, vcache: Optional[torch.Tensor],
                          block_table: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
                          scale: float, softcap: float, sink: bool, slopes: Optional[torch.Tensor], window: int,
-                         batch) -> None:
+                         batch, dist_a: Optional[torch.Tensor] = None, dist_b: Optional[torch.Tensor] = None,
+                         sinks: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
         """out[r, h] = sum_j p_j v_j over the cached positions j <= pos[r] of row r's sequence (from pos -
         window + 1 on when window > 0) with s_j = (q[r, h] . k_j) * scale, then s_j <- softcap * tanh(s_j /
         softcap) when softcap > 0, then s_j <- s_j - slopes[h] * (pos[r] - j) when slopes are given, and
-        p_j = exp(s_j) / (sum exp(s) + (1 if sink else 0)).  ``vcache`` None: the values are the keys."""
+        p_j = exp(s_j) / (sum exp(s) + (1 if sink else 0)).  ``vcache`` None: the values are the keys.
+        ``dist_a``, ``dist_b`` [heads]: s_j <- s_j - dist_a[h] * ln(1 + dist_b[h] * (pos[r] - j)) as well.  ``sinks``
+        [heads]: with ``sink``, exp(sinks[h]) joins the denominator instead of 1.  ``keep_first``: with a window,
+        the keys j < keep_first are seen too."""
         n = q.shape[0]
         _need(q, self.act_dtype, "scored_attention q", 2)
         _need(out, self.act_dtype, "scored_attention out", 2)
@@ -1051,6 +1081,14 @@ class KernelOps:
         if q.shape[1] != heads * dim or tuple(out.shape) != (n, heads * vdim) or kcache.shape[1] != kv_heads or \
                 kcache.shape[3] != dim:
             raise KernelError("scored_attention: shapes do not fit the heads")
+        if (dist_a is None) != (dist_b is None):
+            raise KernelError("scored_attention: the distance term needs both numbers per head")
+        for t_, what in ((dist_a, "dist_a"), (dist_b, "dist_b"), (sinks, "sinks")):
+            if t_ is not None:
+                _need(t_, torch.float32, "scored_attention " + what, 1)
+                if t_.shape[0] != heads:
+                    raise KernelError(f"scored_attention: {what} is not one number per head")
+        tail = (_p(dist_a), _p(dist_b), _p(sinks), _c_int(int(keep_first)))
         tc_rows = self._scored_mma_rows(heads // kv_heads, dim, vdim)
         if tc_rows and (not hasattr(batch, "tile_sets") or tc_rows in batch.tile_sets):
             # The serving precision's tensor-core kernel.  Contexts beyond 256 keys are walked in spans
@@ -1067,7 +1105,8 @@ class KernelOps:
                         _c_int(block_table.shape[1]), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count), _p(batch.seq_pos0),
                         _p(batch.seq_row0), _p(out), _c_int(out.shape[1]), _c_int(heads), _c_int(kv_heads), _c_int(dim),
                         _c_int(vdim), _c_int(kcache.shape[2]), _c_float(scale), _c_float(softcap), _c_int(int(bool(sink))),
-                        _p(slopes), _c_int(window), _c_int(n), _c_int(spans), _p(scratch), self._stream(), launches=launches)
+                        _p(slopes), _c_int(window), _c_int(n), _c_int(spans), _p(scratch), *tail, self._stream(),
+                        launches=launches)
             return
         fn = getattr(self._mixers_lib(), f"bw_{self.kind}_scored_attention_tile_rows")
         t_seq, t_row0, t_rows, t_count = batch.query_tiles(int(fn(_c_int(heads // kv_heads))))
@@ -1075,7 +1114,7 @@ class KernelOps:
                     _c_int(block_table.shape[1]), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count), _p(batch.seq_pos0),
                     _p(batch.seq_row0), _p(out), _c_int(out.shape[1]), _c_int(heads), _c_int(kv_heads), _c_int(dim),
                     _c_int(vdim), _c_int(kcache.shape[2]), _c_float(scale), _c_float(softcap), _c_int(int(bool(sink))),
-                    _p(slopes), _c_int(window), self._stream())
+                    _p(slopes), _c_int(window), *tail, self._stream())
 
     def gla_scan(self, u: torch.Tensor, z: torch.Tensor, bias: torch.Tensor, tau: float, state: torch.Tensor,
                  norm_w: torch.Tensor, eps: float, out: torch.Tensor, heads: int, dim: int, vdim: int, q_scale: float,
@@ -1105,6 +1144,146 @@ class KernelOps:
                     _c_float(eps), _p(scratch), _p(out), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count),
                     _p(batch.seq_pos0), _p(batch.seq_slot), _c_int(n), _c_int(heads), _c_int(dim), _c_int(vdim),
                     _c_float(q_scale), self._stream(), launches=2)
+
+    # -- kernels on the residual stream that only some blocks use (their library is loaded at first use) -------
+    def _stream_lib(self):
+        lib = getattr(self, "_streamlib", None)
+        if lib is None:
+            path = build.ensure_built(f"{self.kind}_stream", (), self._verbose_build)
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+            lib.bw_last_error.restype = ctypes.c_char_p
+            if self._failure_word is not None:
+                lib.bw_set_failure_word(_p(self._failure_word))
+            self._streamlib = lib
+            self._stream_fns = {}
+        return lib
+
+    def _scall(self, name: str, *args, launches: int = 1) -> None:
+        lib = self._stream_lib()
+        fn = self._stream_fns.get(name)
+        if fn is None:
+            fn = getattr(lib, f"bw_{self.kind}_{name}")
+            fn.restype = _c_int
+            self._stream_fns[name] = fn
+        rc = fn(*args)
+        if rc != 0:
+            raise KernelError(f"{name} failed ({rc}): " + lib.bw_last_error().decode("utf-8", "replace"))
+        self.launches += launches
+
+    def embed_pair(self, table: torch.Tensor, pair_table: torch.Tensor, batch, last_token: torch.Tensor, out: torch.Tensor,
+                   scale: float, buckets: int, mul_prev: int, mul_cur: int) -> None:
+        """out[r] = table[token] * scale + pair_table[row], row = (previous token * mul_prev + token * mul_cur) mod
+        buckets, and row ``buckets`` at position 0.  The previous token of a sequence's first row of the step is
+        ``last_token[slot]`` (int32 [slots, 1])."""
+        n, width = out.shape
+        _need(out, torch.float32, "embed_pair out", 2)
+        _need(table, self.act_dtype, "embed_pair table", 2)
+        _need(pair_table, self.act_dtype, "embed_pair pair_table", 2)
+        _need(last_token, torch.int32, "embed_pair last_token")
+        if table.shape[1] != width or tuple(pair_table.shape) != (buckets + 1, width):
+            raise KernelError("embed_pair: the tables are not [vocab, width] and [buckets + 1, width]")
+        self._scall("embed_pair", _p(table), _p(pair_table), _p(batch.tokens), _p(batch.pos), _p(batch.row_seq),
+                    _p(batch.seq_row0), _p(batch.seq_slot), _p(last_token), _p(out), _c_int(n), _c_int(width), _c_float(scale),
+                    _c_int(buckets), _c_int(mul_prev), _c_int(mul_cur), self._stream())
+
+    def last_token_update(self, batch, last_token: torch.Tensor, seq_tiles) -> None:
+        """last_token[slot of s] = the last token of every sequence s of the step (``seq_tiles``: one tile per sequence)."""
+        _need(last_token, torch.int32, "last_token_update last_token")
+        t_seq, t_row0, t_rows, t_count = seq_tiles
+        self._scall("last_token_update", _p(batch.tokens), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count),
+                    _p(batch.seq_slot), _p(last_token), self._stream())
+
+    def norm_conv(self, x: torch.Tensor, weight: torch.Tensor, eps: float, taps_t: torch.Tensor, state: Optional[torch.Tensor],
+                  state_col0: int, batch, out: torch.Tensor, normed: torch.Tensor, normed_col0: int) -> None:
+        """h = rmsnorm(x) * weight; out = h + conv(h) with conv(h)_t = sum_j taps_t[j] * h_(t - taps + 1 + j) per channel
+        (``taps_t`` float32 [taps, width]); rows before the step's first of a sequence are read from ``state``
+        [slots, taps - 1, state columns] at columns state_col0 .., zeros before position 0.  ``normed`` (float32 [n,
+        columns], written at columns normed_col0 ..) receives h, for ``conv_state_update``."""
+        n, width = out.shape
+        _need(x, torch.float32, "norm_conv x", 2)
+        _need(weight, torch.float32, "norm_conv weight", 1)
+        _need(taps_t, torch.float32, "norm_conv taps", 2)
+        _need(out, self.act_dtype, "norm_conv out", 2)
+        _need(normed, torch.float32, "norm_conv normed", 2)
+        taps = taps_t.shape[0]
+        if tuple(x.shape) != (n, width) or weight.shape[0] != width or taps_t.shape[1] != width or normed.shape[0] != n or \
+                normed_col0 + width > normed.shape[1]:
+            raise KernelError("norm_conv: shapes differ")
+        state_cols = 0
+        if state is not None:
+            _need(state, torch.float32, "norm_conv state", 3)
+            state_cols = state.shape[2]
+            if state.shape[1] != taps - 1 or state_col0 + width > state_cols:
+                raise KernelError("norm_conv: the state is not [slots, taps - 1, columns]")
+        self._scall("norm_conv", _p(x), _p(weight), _c_float(eps), _p(taps_t), _c_int(taps), _p(state), _c_int(state_cols),
+                    _c_int(state_col0), _p(batch.pos), _p(batch.row_seq), _p(batch.seq_row0), _p(batch.seq_slot), _p(out),
+                    _p(normed), _c_int(normed.shape[1]), _c_int(normed_col0), _c_int(n), _c_int(width), self._stream())
+
+    def scaled_add(self, x: torch.Tensor, scale: Optional[torch.Tensor], d: Optional[torch.Tensor],
+                   rounded: Optional[torch.Tensor] = None) -> None:
+        """x += scale * d column by column (float32; nothing is added without ``scale``); ``rounded``
+        (act_dtype) receives the summed rows as well."""
+        n, width = x.shape
+        _need(x, torch.float32, "scaled_add x", 2)
+        if (scale is None) != (d is None):
+            raise KernelError("scaled_add: the factors and the rows come together")
+        if scale is not None:
+            _need(scale, torch.float32, "scaled_add scale", 1)
+            _need(d, torch.float32, "scaled_add d", 2)
+            if scale.shape[0] != width or tuple(d.shape) != (n, width):
+                raise KernelError("scaled_add: shapes differ")
+        if rounded is not None:
+            _need(rounded, self.act_dtype, "scaled_add rounded", 2)
+            if tuple(rounded.shape) != (n, width):
+                raise KernelError("scaled_add: shapes differ")
+        self._scall("scaled_add", _p(x), _p(scale), _p(d), _p(rounded), _c_int(n), _c_int(width), self._stream())
+
+    def token_gate(self, t: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Tensor, out: torch.Tensor) -> None:
+        """out[r] = gelu_tanh(t[r]) * table[tokens[r], col0 : col0 + dim] (t float32 [n, dim], out act_dtype)."""
+        n, dim = t.shape
+        _need(t, torch.float32, "token_gate t", 2)
+        _need(table, self.act_dtype, "token_gate table", 2)
+        _need(tokens, torch.int32, "token_gate tokens")
+        _need(out, self.act_dtype, "token_gate out", 2)
+        if tuple(out.shape) != (n, dim) or col0 < 0 or col0 + dim > table.shape[1]:
+            raise KernelError("token_gate: shapes differ")
+        self._scall("token_gate", _p(t), _p(table), _c_int(table.shape[1]), _c_int(col0), _p(tokens), _p(out), _c_int(n),
+                    _c_int(dim), self._stream())
+
+    def normed_add_mix(self, x: torch.Tensor, y: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+                       mult: float, history: Optional[torch.Tensor], index: int, mix: Optional[torch.Tensor]) -> None:
+        """x[r] += mult * y[r] / sqrt(mean(y[r]^2) + eps) * weight (skipped without ``y``); then, with ``history``
+        (float32 [n, entries * width]): entry ``index`` of the row's history = x[r], and x[r] = sum_j mix[j] *
+        history entry j, j = 0 .. index (mix float32 [index + 1])."""
+        n, width = x.shape
+        _need(x, torch.float32, "normed_add_mix x", 2)
+        if y is not None:
+            _need(y, torch.float32, "normed_add_mix y", 2)
+            _need(weight, torch.float32, "normed_add_mix weight", 1)
+            if tuple(y.shape) != (n, width) or weight.shape[0] != width:
+                raise KernelError("normed_add_mix: shapes differ")
+        entries = 0
+        if history is not None:
+            _need(history, torch.float32, "normed_add_mix history", 2)
+            _need(mix, torch.float32, "normed_add_mix mix", 1)
+            entries = history.shape[1] // width
+            if history.shape[0] != n or history.shape[1] % width or mix.shape[0] != index + 1 or index >= entries:
+                raise KernelError("normed_add_mix: the history does not fit")
+        self._scall("normed_add_mix", _p(x), _p(y), _p(weight), _c_float(eps), _c_float(mult), _p(history), _c_int(entries),
+                    _c_int(index), _p(mix), _c_int(n), _c_int(width), self._stream())
+
+    def copy_history(self, x: torch.Tensor, history: torch.Tensor) -> None:
+        """Entry 0 of every row's history (float32 [n, entries * width]) = x[r]."""
+        n, width = x.shape
+        _need(x, torch.float32, "copy_history x", 2)
+        _need(history, torch.float32, "copy_history history", 2)
+        if history.shape[0] != n or history.shape[1] % width:
+            raise KernelError("copy_history: the history does not fit")
+        self._scall("copy_history", _p(x), _p(history), _c_int(history.shape[1] // width), _c_int(n), _c_int(width),
+                    self._stream())
 
 
 _OPS = {}

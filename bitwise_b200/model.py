@@ -90,6 +90,8 @@ class Model:
                 else:
                     t = torch.empty(s.shape, dtype=torch.float32, device=device)
                     t.normal_(0.0, std, generator=gen)
+                    if s.init == "positive":
+                        t.abs_()
                     state[s.name] = t if s.kind == KEEP32 else t.to(tdt)
         else:
             tensors = random_tensors(specs, seed, torch.float32 if dtype == "float32" else torch.bfloat16,

@@ -35,13 +35,15 @@ class DecoderModel:
     def __init__(self, config, embedding: TokenEmbedding, blocks: Sequence, head: OutputHead,
                  schedule: Optional[Sequence[LayerRun]] = None,
                  position_encodings: Sequence[PositionEncoding] = (),
-                 block_prefix: str = "model.layers.{}", embed_prefix: str = "model"):
+                 block_prefix: str = "model.layers.{}", embed_prefix: str = "model", shared_parts: Sequence = ()):
+        """``shared_parts``: parts with weights that several blocks use (a table that every layer reads a
+        slice of); their tensors are declared and loaded once, with ``embed_prefix``."""
         self.config = config
         self.embedding = embedding
         self.blocks = list(blocks)
         self.head = head
         self.schedule = list(schedule) if schedule is not None else sequential_schedule(len(self.blocks))
-        self.position_encodings = list(position_encodings)
+        self.position_encodings = list(position_encodings) + list(shared_parts)
         self.block_prefix, self.embed_prefix = block_prefix, embed_prefix
         self.dtype: Optional[str] = None
         self.device = None
@@ -75,6 +77,11 @@ class DecoderModel:
         self.cache_entries = sorted(owners)
         if self.cache_entries != list(range(len(self.cache_entries))):
             raise ValueError("cache entries must be numbered 0..n-1 without gaps")
+        # state that the embedding keeps per request (a previous token) takes one more entry, behind the runs'
+        self.embedding_state = None
+        if getattr(self.embedding, "state_need", lambda: None)() is not None:
+            self.embedding_state = len(self.cache_entries)
+            self.cache_entries.append(self.embedding_state)
 
     # -- what the cache manager needs to know -----------------------------------------
     def cache_needs(self) -> List[object]:
@@ -85,6 +92,8 @@ class DecoderModel:
                 needs[run.cache] = self.blocks[run.block].cache_need()
             if run.state is not None:
                 needs[run.state] = self.blocks[run.block].state_need()
+        if self.embedding_state is not None:
+            needs[self.embedding_state] = self.embedding.state_need()
         return needs
 
     # -- parameters --------------------------------------------------------------------
@@ -133,7 +142,7 @@ class DecoderModel:
         parts = [self.embedding, self.head, self.head.norm] + list(self.position_encodings)
         for b in self.blocks:
             parts += [b, b.mixer, b.feed_forward, b.mixer_norm, b.ffn_norm, getattr(b, "mixer_post", None),
-                      getattr(b, "ffn_post", None)]
+                      getattr(b, "ffn_post", None), getattr(b, "side", None)]
         return all(getattr(p, "graph_safe", False) for p in parts if p is not None)
 
     def reserve_positions(self, positions: int) -> None:
@@ -146,9 +155,13 @@ class DecoderModel:
         """Run the step's rows through every scheduled layer; returns float32 logits
         [wanted rows, vocab] or None.  ``cache_views[e]`` is the view of cache entry e."""
         x = ctx.workspace.rows("stream", ctx.n, self.embedding.width, torch.float32)
-        self.embedding.forward(ctx, x)
+        if self.embedding_state is not None:
+            self.embedding.forward(ctx, x, cache_views[self.embedding_state])
+        else:
+            self.embedding.forward(ctx, x)
         for pe in self.position_encodings:
-            pe.on_embed(ctx, x)
+            if hasattr(pe, "on_embed"):
+                pe.on_embed(ctx, x)
         for run in self.schedule:
             view = cache_views[run.cache]
             if not run.owns_cache and hasattr(view, "writable"):

@@ -2,7 +2,8 @@ from .attention import GQAAttention
 from .base import (FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, FeedForward, Mixer, Norm, PagedKVNeed,
                    PagedKVView, PagedLatentNeed, PagedLatentView, Part, PositionEncoding, SlotStateNeed, SlotStateView, StepContext, Workspace,
                    register_feed_forward, register_mixer, register_norm, register_position_encoding)
-from .block import ParallelBlock, PreNormBlock, SandwichBlock
+from .block import DepthMix, ParallelBlock, PreNormBlock, SandwichBlock, ScaledResidualBlock
+from .token_side import TokenSide, TokenSideTable
 from .embedding import OutputHead, TokenEmbedding
 from .mlp import SwiGLU
 from .latent_attention import LatentAttention

@@ -28,11 +28,13 @@ class PagedKVNeed:
     """Keys and values that grow with the position, kept in pages.
     ``window`` = None keeps every key; an integer keeps the last ``window`` positions.
     ``v_dim``: the size of a value where it differs from a key's (None: ``head_dim``); 0 keeps no
-    values at all (a mixer whose values are its keys)."""
+    values at all (a mixer whose values are its keys).  ``keep_first``: with a window, the first
+    ``keep_first`` positions of a request stay in the cache as well."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_dim: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

@@ -12,41 +12,69 @@ from typing import Dict, List, Optional
 import torch
 
 from ..weights.loader import MATRIX, ParamSpec
-from .base import Norm, Part, StepContext
+from .base import Norm, Part, SlotStateNeed, StepContext
 
 
 class TokenEmbedding(Part):
     graph_safe = True  # kernels only: a step through this part can be captured
 
     def __init__(self, vocab: int, width: int, name: str = "embed_tokens", tensor: Optional[str] = None,
-                 norm: Optional[Norm] = None, norm_tensor: Optional[str] = None, scale: float = 1.0):
+                 norm: Optional[Norm] = None, norm_tensor: Optional[str] = None, scale: float = 1.0,
+                 pair_table: Optional[str] = None, pair_buckets: int = 0, pair_mul_prev: int = 0, pair_mul_cur: int = 0):
         """``tensor``: the table's full name where it is not ``<prefix>.<name>.weight``.  ``norm``:
         a norm applied to the embedded rows in place on the stream, its weight named ``norm_tensor``.
-        ``scale``: a constant that the embedded rows are multiplied by (in 32-bit)."""
+        ``scale``: a constant that the embedded rows are multiplied by (in 32-bit).  ``pair_table``:
+        the name of a second table ``[pair_buckets + 1, width]`` whose row ``(previous token *
+        pair_mul_prev + token * pair_mul_cur) mod pair_buckets`` is added (unscaled), the last row
+        for a sequence's first token; the previous token is kept per request in a state slot."""
         self.vocab, self.width, self.name = vocab, width, name
         self.scale = float(scale)
         self.tensor, self.norm, self.norm_tensor = tensor, norm, norm_tensor
         self.table: Optional[torch.Tensor] = None
+        self.pair_name = pair_table
+        self.pair_buckets, self.pair_mul_prev, self.pair_mul_cur = int(pair_buckets), int(pair_mul_prev), int(pair_mul_cur)
+        if pair_table is not None and self.pair_buckets <= 0:
+            raise ValueError("a second table needs a positive number of buckets")
+        self.pair: Optional[torch.Tensor] = None
+
+    def state_need(self):
+        """With a second table: the request's last token, one int32 per slot."""
+        return SlotStateNeed((1,), torch.int32) if self.pair_name is not None else None
+
+    def query_tile_rows(self, ops=None):
+        from .scored_attention import SEQUENCE_TILE
+        return [SEQUENCE_TILE] if self.pair_name is not None else []
 
     def tensor_name(self, prefix: str) -> str:
         return self.tensor if self.tensor is not None else f"{prefix}.{self.name}.weight"
 
     def param_specs(self, prefix: str) -> List[ParamSpec]:
         specs = [ParamSpec(self.tensor_name(prefix), (self.vocab, self.width), MATRIX)]
+        if self.pair_name is not None:
+            specs.append(ParamSpec(self.pair_name, (self.pair_buckets + 1, self.width), MATRIX))
         if self.norm is not None:
             specs += self.norm.param_specs(self.norm_tensor)
         return specs
 
     def load_params(self, state: Dict[str, torch.Tensor], prefix: str) -> None:
         self.table = state[self.tensor_name(prefix)]
+        if self.pair_name is not None:
+            self.pair = state[self.pair_name]
         if self.norm is not None:
             self.norm.load_params(state, self.norm_tensor)
 
     def param_bytes(self) -> int:
-        return self.table.numel() * self.table.element_size() + (self.norm.param_bytes() if self.norm else 0)
+        pair = self.pair.numel() * self.pair.element_size() if self.pair is not None else 0
+        return self.table.numel() * self.table.element_size() + pair + (self.norm.param_bytes() if self.norm else 0)
 
-    def forward(self, ctx: StepContext, x: torch.Tensor) -> None:
-        if self.scale != 1.0:
+    def forward(self, ctx: StepContext, x: torch.Tensor, state=None) -> None:
+        """``state``: the ``SlotStateView`` of ``state_need`` (the requests' last tokens)."""
+        if self.pair is not None:
+            from .scored_attention import SEQUENCE_TILE
+            ctx.ops.embed_pair(self.table, self.pair, ctx, state.state, x, self.scale, self.pair_buckets,
+                               self.pair_mul_prev, self.pair_mul_cur)
+            ctx.ops.last_token_update(ctx, state.state, ctx.query_tiles(SEQUENCE_TILE))
+        elif self.scale != 1.0:
             ctx.ops.embed_rows(self.table, ctx.tokens, x, scale=self.scale)
         else:
             ctx.ops.embed_rows(self.table, ctx.tokens, x)

@@ -24,9 +24,10 @@ from ..weights.loader import KEEP32, MATRIX, ParamSpec
 from .base import FeedForward, StepContext, register_feed_forward
 
 
-class ClampedGLU:
-    """gate / up / down with the clamped activation: the shared expert, and the form of every
-    routed one."""
+class ClampedGLU(FeedForward):
+    """gate / up / down with the clamped activation: the shared expert, the form of every
+    routed one, and a dense feed-forward of its own."""
+    graph_safe = True  # kernels only
 
     def __init__(self, width: int, inner: int, limit: float, alpha: float):
         self.width, self.inner, self.limit, self.alpha = width, inner, float(limit), float(alpha)
@@ -45,13 +46,14 @@ class ClampedGLU:
     def param_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
-    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor) -> None:
+    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, accumulate: bool = True) -> None:
+        """``accumulate`` False: the output is written to ``x`` (float32) instead of added to it."""
         ops, n = ctx.ops, ctx.n
         gate_up = ctx.workspace.rows("glu_gate_up", n, 2 * self.inner, ctx.act_dtype)
         ops.linear(xn, self.w_gate_up, gate_up)
         h = ctx.workspace.rows("glu_h", n, self.inner, ctx.act_dtype)
         ops.glu_clamped(gate_up, h, self.limit, self.alpha)
-        ops.linear(h, self.w_down, x, residual=x)
+        ops.linear(h, self.w_down, x, residual=x if accumulate else None)
 
 
 class RoutedFFN(FeedForward):
@@ -59,7 +61,13 @@ class RoutedFFN(FeedForward):
 
     def __init__(self, width: int, experts: int, top: int, inner: int, limit: float, alpha: float,
                  weight_scale: float = 1.0, groups: int = 1, keep_groups: int = 1, correction: bool = True,
-                 shared: Optional[ClampedGLU] = None):
+                 shared: Optional[ClampedGLU] = None, scoring: str = "sigmoid", activation: str = "clamped"):
+        """``scoring``: "sigmoid" (the weights are the chosen experts' sigmoid scores) or "softmax_top" (the
+        largest logits are chosen and the weights are the softmax over the chosen logits only).
+        ``activation``: "clamped" (``limit``, ``alpha``) or "silu" (``silu(gate) * up``)."""
+        if scoring not in ("sigmoid", "softmax_top") or activation not in ("clamped", "silu"):
+            raise ValueError(f"unknown scoring {scoring!r} or activation {activation!r}")
+        self.scoring, self.activation = scoring, activation
         if experts <= 0 or groups <= 0 or experts % groups:
             raise ValueError(f"{experts} experts do not form {groups} equal groups")
         if not (0 < keep_groups <= groups) or not (0 < top <= keep_groups * (experts // groups)):
@@ -101,7 +109,14 @@ class RoutedFFN(FeedForward):
     def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor) -> None:
         self.forward_sum(ctx, xn, None, x)
 
-    def forward_sum(self, ctx: StepContext, xn: torch.Tensor, d: Optional[torch.Tensor], x: torch.Tensor) -> None:
+    def forward_scaled(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, scale: torch.Tensor) -> None:
+        """``x += scale * feed_forward(xn)`` column by column (``scale`` float32 [width])."""
+        if self.shared is not None:
+            raise NotImplementedError("a scaled sum with a shared expert")
+        self.forward_sum(ctx, xn, None, x, scale=scale)
+
+    def forward_sum(self, ctx: StepContext, xn: torch.Tensor, d: Optional[torch.Tensor], x: torch.Tensor,
+                    scale: Optional[torch.Tensor] = None) -> None:
         """``x += d + feed_forward(xn)``; ``d`` (float32 rows, or None) is used as scratch."""
         ops, ws, n, top = ctx.ops, ctx.workspace, ctx.n, self.top
         act = ctx.act_dtype
@@ -111,7 +126,8 @@ class RoutedFFN(FeedForward):
         ops.linear(xn, self.w_router, z)
         chosen = ws.rows("route_chosen", n, top, torch.int32)
         weights = ws.rows("route_weights", n, top, torch.float32)
-        ops.route(z, self.correction, self.groups, self.keep_groups, top, self.weight_scale, chosen, weights)
+        ops.route(z, self.correction, self.groups, self.keep_groups, top, self.weight_scale, chosen, weights,
+                  softmax_top=self.scoring == "softmax_top")
         lists = ws.rows("route_lists", 3, self.experts + 1, torch.int32)
         order = ws.rows("route_order", n, top, torch.int32)
         place = ws.rows("route_place", n, top, torch.int32)
@@ -124,13 +140,16 @@ class RoutedFFN(FeedForward):
             sorted_x = ws.rows("routed_x", n, top * self.width, act).view(pairs, self.width)
         ops.grouped_linear(xn, self.w_gate_up, gate_up, pairs, lists=grouped, order_div=top, sorted_x=sorted_x)
         h = ws.rows("routed_h", n, top * self.inner, act).view(pairs, self.inner)
-        ops.glu_clamped(gate_up, h, self.limit, self.alpha)
+        if self.activation == "silu":
+            ops.swiglu(gate_up, h)
+        else:
+            ops.glu_clamped(gate_up, h, self.limit, self.alpha)
         y = ws.rows("routed_y", n, top * self.width, torch.float32).view(pairs, self.width)
         ops.grouped_linear(h, self.w_down, y, pairs, lists=grouped, gather=False)
         # the shared expert adds into d (or, without d, into the stream), then everything into the stream
         if self.shared is not None:
             self.shared.forward(ctx, xn, d if d is not None else x)
-        ops.combine(x, d, y, place, weights, top)
+        ops.combine(x, d, y, place, weights, top, scale=scale)
 
 
 register_feed_forward("routed", RoutedFFN)

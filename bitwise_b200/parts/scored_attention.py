@@ -2,6 +2,10 @@
 
 Before the scores, each on or off by a constructor argument:
 
+* biases of the q, k and v projections (``bias``; tensors ``<name>.b``), added in 32-bit;
+* ``value_mix``: the layer's values become ``(1 - lambda) v + lambda v_first`` with ``v_first`` the values
+  that the model's first such layer (``"source"``) formed for the same token and ``lambda`` the
+  layer's scalar tensor (``"mix"``); the mixed values are what is cached;
 * a short causal convolution over time on every channel of q, k and v, directly after the
   projection: ``y_t = sum_j w[:, j] * u_(t - taps + 1 + j)``, zeros before the sequence's start.
   The last ``taps - 1`` projected rows of a request are its state, kept in a state slot;
@@ -13,8 +17,11 @@ On the scores ``s = (q . k) * scale``:
 
 * ``softcap``: ``s <- cap * tanh(s / cap)``;
 * ``slopes``: ``s <- s - slope_h * (i - j)`` for query position i and key position j;
-* ``window``: position i sees the keys j with ``0 <= i - j < window`` (every j <= i without);
-* ``sink``: one is added to the softmax's denominator (a key of score 0 that has no value).
+* ``distance_log``: ``s <- s - a_h * ln(1 + b_h * (i - j))`` with two learned numbers per head;
+* ``window``: position i sees the keys j with ``0 <= i - j < window`` (every j <= i without), and
+  with ``keep_first`` also the keys ``j < keep_first``, at their true distance;
+* ``sink``: one is added to the softmax's denominator (a key of score 0 that has no value);
+  ``sink="learned"``: ``exp(sink_h)`` with a learned number per head instead.
 
 ``values_are_keys``: there is no value projection and nothing but the keys is cached; the
 weighted sum runs over the keys as projected.  ``shares_cache``: the layer has no key and value
@@ -43,13 +50,15 @@ def distance_slopes(heads: int, exponent: float = 8.0) -> List[float]:
 class ScoredAttention(Mixer):
     graph_safe = True  # kernels only; launches depend on the step's sizes and ctx.max_keys
 
-    NAMES = {"q": "q", "k": "k", "v": "v", "out": "o", "conv": ".conv", "norm": ".norm"}
+    NAMES = {"q": "q", "k": "k", "v": "v", "out": "o", "conv": ".conv", "norm": ".norm", "bias": ".b", "vmix": "vmix",
+             "dist_a": "r1", "dist_b": "r2", "sink": "sink"}
 
     def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, eps: float = 1e-6,
                  conv_taps: int = 0, qk_norm: bool = False, position: Optional[PositionEncoding] = None, rot_dims: int = 0,
                  softcap: Optional[float] = None, sink: bool = False, slopes: Optional[Sequence[float]] = None,
                  window: Optional[int] = None, values_are_keys: bool = False, shares_cache: bool = False,
-                 names: Optional[Dict[str, str]] = None):
+                 names: Optional[Dict[str, str]] = None, bias: bool = False, distance_log: bool = False,
+                 keep_first: int = 0, value_mix: Optional[str] = None):
         if heads % kv_heads:
             raise ValueError(f"{heads} heads are not a multiple of {kv_heads} key/value heads")
         if values_are_keys and vdim != dim:
@@ -58,11 +67,18 @@ class ScoredAttention(Mixer):
             raise ValueError("one slope per head is needed")
         if rot_dims % 2 or rot_dims > dim:
             raise ValueError(f"{rot_dims} turned entries do not fit a head of {dim}")
+        if value_mix not in (None, "source", "mix"):
+            raise ValueError(f"value_mix is None, 'source' or 'mix', not {value_mix!r}")
+        if value_mix and (values_are_keys or shares_cache):
+            raise ValueError("values can only be mixed where the layer forms values of its own")
         self.width, self.heads, self.kv_heads, self.dim, self.vdim = width, heads, kv_heads, dim, vdim
         self.scale, self.eps = float(scale), float(eps)
         self.taps = int(conv_taps or 0)  # 0: no convolution; 1: a factor per channel and no state
         self.qk_norm, self.position, self.rot_dims = qk_norm, position, rot_dims
         self.softcap, self.sink, self.window = softcap, bool(sink), window
+        self.learned_sink = sink == "learned"
+        self.bias, self.distance_log, self.value_mix = bool(bias), bool(distance_log), value_mix
+        self.keep_first = int(keep_first or 0) if window else 0
         self.slopes_host = [float(s) for s in slopes] if slopes is not None else None
         self.values_are_keys, self.shares_cache = values_are_keys, shares_cache
         self.names = dict(self.NAMES, **(names or {}))
@@ -71,10 +87,12 @@ class ScoredAttention(Mixer):
         self.v_cols = 0 if shares_cache or values_are_keys else kv_heads * vdim
         self.cols = self.q_cols + self.k_cols + self.v_cols
         self.w_in = self.w_o = self.conv_w = self.conv_wt = self.q_norm = self.k_norm = self.slopes = None
+        self.b_in = self.dist_a = self.dist_b = self.sinks = self.vmix = None
 
     # -- what the cache keeps --------------------------------------------------------------
     def cache_need(self):
-        return PagedKVNeed(self.kv_heads, self.dim, self.window, v_dim=0 if self.values_are_keys else self.vdim)
+        return PagedKVNeed(self.kv_heads, self.dim, self.window, v_dim=0 if self.values_are_keys else self.vdim,
+                           keep_first=self.keep_first)
 
     def state_need(self):
         """The convolution's inputs of the last ``taps - 1`` positions, for every channel it runs on."""
@@ -105,10 +123,19 @@ class ScoredAttention(Mixer):
         specs = []
         for name, cols, size, normed in self._projections():
             specs.append(ParamSpec(f"{prefix}.{name}", (cols, self.width), MATRIX))
+            if self.bias:
+                specs.append(ParamSpec(f"{prefix}.{name}{n['bias']}", (cols,), KEEP32))
             if self.taps:
                 specs.append(ParamSpec(f"{prefix}.{name}{n['conv']}", (cols, self.taps), KEEP32))
             if self.qk_norm and normed:
                 specs.append(ParamSpec(f"{prefix}.{name}{n['norm']}", (size,), KEEP32, init="ones"))
+        if self.value_mix:  # (the first such layer has the tensor too and no use for it)
+            specs.append(ParamSpec(f"{prefix}.{n['vmix']}", (), KEEP32))
+        if self.distance_log:
+            specs += [ParamSpec(f"{prefix}.{n['dist_a']}", (self.heads,), KEEP32),
+                      ParamSpec(f"{prefix}.{n['dist_b']}", (self.heads,), KEEP32, init="positive")]
+        if self.learned_sink:
+            specs.append(ParamSpec(f"{prefix}.{n['sink']}", (self.heads,), KEEP32))
         specs.append(ParamSpec(f"{prefix}.{n['out']}", (self.width, self.heads * self.vdim), MATRIX))
         return specs
 
@@ -124,11 +151,20 @@ class ScoredAttention(Mixer):
             self.q_norm = state[f"{prefix}.{n['q']}{n['norm']}"]
             self.k_norm = None if self.shares_cache else state[f"{prefix}.{n['k']}{n['norm']}"]
         self.w_o = state[f"{prefix}.{n['out']}"]
+        if self.bias:
+            self.b_in = torch.cat([state[f"{prefix}.{name}{n['bias']}"] for name, _, _, _ in proj], 0).contiguous()
+        if self.value_mix == "mix":
+            self.vmix = state[f"{prefix}.{n['vmix']}"].reshape(1).contiguous()
+        if self.distance_log:
+            self.dist_a, self.dist_b = state[f"{prefix}.{n['dist_a']}"], state[f"{prefix}.{n['dist_b']}"]
+        if self.learned_sink:
+            self.sinks = state[f"{prefix}.{n['sink']}"]
         if self.slopes_host is not None:
             self.slopes = torch.tensor(self.slopes_host, dtype=torch.float32, device=self.w_o.device)
 
     def param_bytes(self) -> int:
-        ts = (self.w_in, self.w_o, self.conv_w, self.q_norm, self.k_norm)  # (the transposed taps are a copy)
+        ts = (self.w_in, self.w_o, self.conv_w, self.q_norm, self.k_norm, self.b_in, self.vmix, self.dist_a, self.dist_b,
+              self.sinks)  # (the transposed taps are a copy)
         return sum(t.numel() * t.element_size() for t in ts if t is not None)
 
     # -- one step --------------------------------------------------------------------------
@@ -143,14 +179,25 @@ class ScoredAttention(Mixer):
         q = ws.rows("scored_q", n, self.q_cols, ctx.act_dtype)
         state = cache.state if self.taps > 1 else None
         writes = cache.writable and not self.shares_cache
+        extra = {}
+        if self.bias:
+            extra["bias"] = self.b_in
+        if self.value_mix and writes:
+            # the first mixing layer's values of the step's rows, in 32-bit, for the layers after it
+            first = ws.rows("mixed_values_first", n, self.v_cols, torch.float32)
+            if self.value_mix == "source":
+                extra["v_keep"] = first
+            else:
+                extra["vmix_src"], extra["vmix_lambda"] = first, self.vmix
         ops.qkv_prepare(u, self.conv_w, state.state if state is not None else None, self.q_norm, self.k_norm, self.eps,
                         cos, sin, ctx, cache.block_table, cache.k, cache.v, q, self.heads,
-                        self.kv_heads if writes else 0, self.dim, self.vdim, conv_wt=self.conv_wt)
+                        self.kv_heads if writes else 0, self.dim, self.vdim, conv_wt=self.conv_wt, **extra)
         if state is not None:
             ops.conv_state_update(u, state.state, ctx, self.taps, ctx.query_tiles(SEQUENCE_TILE))
         mixed = ws.rows("scored_mixed", n, self.heads * self.vdim, ctx.act_dtype)
         ops.scored_attention(q, cache.k, cache.v, cache.block_table, mixed, self.heads, self.kv_heads, self.dim, self.vdim,
-                             self.scale, self.softcap or 0.0, self.sink, self.slopes, self.window or 0, ctx)
+                             self.scale, self.softcap or 0.0, self.sink, self.slopes, self.window or 0, ctx,
+                             dist_a=self.dist_a, dist_b=self.dist_b, sinks=self.sinks, keep_first=self.keep_first)
         ops.linear(mixed, self.w_o, x, residual=x if accumulate else None)
 
 

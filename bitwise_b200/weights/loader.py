@@ -32,7 +32,7 @@ class ParamSpec:
     shape: Tuple[int, ...]
     kind: str = MATRIX
     optional: bool = False
-    init: str = "normal"  # how the random-weights mode fills it: "normal", "ones" or "zeros"
+    init: str = "normal"  # how the random-weights mode fills it: "normal", "positive" (|normal|), "ones" or "zeros"
 
 
 class WeightError(ValueError):

@@ -89,6 +89,8 @@ def random_tensors(specs: Iterable[ParamSpec], seed: int, dtype: torch.dtype = t
                 v = v + uniform_values(seed, s.name, numel, -norm_jitter, norm_jitter)
         else:
             v = normal_values(seed, s.name, numel, std)
+            if s.init == "positive":  # a number that must not be negative (a factor inside a logarithm)
+                v = np.abs(v)
         t = torch.from_numpy(v.astype(np.float32)).reshape(s.shape)
         store = torch.float32 if (s.kind == KEEP32 and dtype == torch.float32) else dtype
         out[s.name] = t.to(store)

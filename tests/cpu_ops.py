@@ -33,9 +33,13 @@ class CpuOps:
         return [max(1, 32 // group)]
 
     def qkv_prepare(self, u, conv_w, conv_state, q_norm, k_norm, eps, cos, sin, ctx, block_table, kcache, vcache, q_out,
-                    heads, write_kv_heads, dim, vdim, conv_wt=None):
+                    heads, write_kv_heads, dim, vdim, conv_wt=None, bias=None, vmix_src=None, vmix_lambda=None, v_keep=None):
         n, cols = u.shape
         page = kcache.shape[2]
+        if bias is not None:
+            u = u + bias
+            if conv_state is not None:
+                conv_state = conv_state + bias
         y = u.clone()
         if conv_w is not None:
             taps = conv_w.shape[1]
@@ -70,6 +74,11 @@ class CpuOps:
         g = write_kv_heads
         k = finish(y[:, heads * dim:(heads + g) * dim], dim, k_norm)
         v = y[:, (heads + g) * dim:].reshape(n, g, vdim) if vcache is not None else None
+        if vmix_src is not None:
+            lam = float(vmix_lambda[0])
+            v = (1.0 - lam) * v + lam * vmix_src.reshape(n, g, vdim)
+        if v_keep is not None:
+            v_keep.copy_(v.reshape(n, -1))
         for r in range(n):
             blk = int(block_table[int(ctx.row_seq[r]), int(p[r]) // page])
             kcache[blk, :, int(p[r]) % page, :] = k[r].to(kcache.dtype)
@@ -92,7 +101,7 @@ class CpuOps:
                     state[slot, j] = old[pos - pos0 + taps - 1]
 
     def scored_attention(self, q, kcache, vcache, block_table, out, heads, kv_heads, dim, vdim, scale, softcap, sink,
-                         slopes, window, ctx):
+                         slopes, window, ctx, dist_a=None, dist_b=None, sinks=None, keep_first=0):
         n = q.shape[0]
         page = kcache.shape[2]
         grp = heads // kv_heads
@@ -100,6 +109,8 @@ class CpuOps:
             p = int(ctx.pos[r])
             lo = max(0, p - window + 1) if window else 0
             idx = torch.arange(lo, p + 1)
+            if window and keep_first and lo > 0:
+                idx = torch.cat([torch.arange(0, min(keep_first, lo)), idx])
             blocks = block_table[int(ctx.row_seq[r])][(idx // page).long()].long()
             slots = (idx % page).long()
             k = kcache[blocks, :, slots, :].float().repeat_interleave(grp, dim=1)
@@ -109,10 +120,102 @@ class CpuOps:
                 s = softcap * torch.tanh(s / softcap)
             if slopes is not None:
                 s = s - slopes[:, None] * (p - idx).float()[None, :]
+            if dist_a is not None:
+                s = s - dist_a[:, None] * torch.log1p(dist_b[:, None] * (p - idx).float()[None, :])
             m = s.max(-1, keepdim=True).values
             e = torch.exp(s - m)
-            den = e.sum(-1, keepdim=True) + (torch.exp(-m) if sink else 0.0)
+            extra = torch.exp((sinks[:, None] if sinks is not None else 0.0) - m) if sink else 0.0
+            den = e.sum(-1, keepdim=True) + extra
             out[r] = torch.einsum("hk,khd->hd", e / den, v).reshape(-1).to(out.dtype)
+
+    # -- kernels on the stream, the second embedding table and the routed feed-forward (stand-ins) --
+    def embed_pair(self, table, pair_table, ctx, last_token, out, scale, buckets, mul_prev, mul_cur):
+        for r in range(out.shape[0]):
+            s, tok = int(ctx.row_seq[r]), int(ctx.tokens[r])
+            row = buckets
+            if int(ctx.pos[r]) > 0:
+                prev = int(ctx.tokens[r - 1]) if r > int(ctx.seq_row0[s]) else int(last_token[int(ctx.seq_slot[s])])
+                row = (prev * mul_prev + tok * mul_cur) % buckets
+            out[r] = table[tok].float() * scale + pair_table[row].float()
+
+    def last_token_update(self, ctx, last_token, tiles):
+        t_seq, t_row0, t_rows, count = tiles
+        for i in range(count):
+            last_token[int(ctx.seq_slot[int(t_seq[i])])] = int(ctx.tokens[int(t_row0[i]) + int(t_rows[i]) - 1])
+
+    def norm_conv(self, x, weight, eps, taps_t, state, state_col0, ctx, out, normed, normed_col0):
+        n, width = out.shape
+        taps = taps_t.shape[0]
+        h = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight
+        normed[:, normed_col0:normed_col0 + width] = h
+        for r in range(n):
+            s = int(ctx.row_seq[r])
+            row0, slot = int(ctx.seq_row0[s]), int(ctx.seq_slot[s])
+            acc = torch.zeros(width)
+            for j in range(taps):
+                back = taps - 1 - j
+                if int(ctx.pos[r]) - back < 0:
+                    continue
+                src = h[r - back] if r - back >= row0 else state[slot, taps - 1 - (row0 - (r - back)), state_col0:state_col0 + width]
+                acc += taps_t[j] * src
+            out[r] = (h[r] + acc).to(out.dtype)
+
+    def scaled_add(self, x, scale, d, rounded=None):
+        if scale is not None:
+            x += scale * d
+        if rounded is not None:
+            rounded.copy_(x.to(rounded.dtype))
+
+    def token_gate(self, t, table, col0, tokens, out):
+        e = table[tokens.long()][:, col0:col0 + t.shape[1]].float()
+        out.copy_((torch.nn.functional.gelu(t, approximate="tanh") * e).to(out.dtype))
+
+    def normed_add_mix(self, x, y, weight, eps, mult, history, index, mix):
+        if y is not None:
+            x += mult * (y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * weight)
+        if history is not None:
+            width = x.shape[1]
+            history[:, index * width:(index + 1) * width] = x
+            x.copy_(sum(mix[j] * history[:, j * width:(j + 1) * width] for j in range(index + 1)))
+
+    def copy_history(self, x, history):
+        history[:, :x.shape[1]] = x
+
+    def glu_clamped(self, gate_up, out, limit, alpha):
+        inter = out.shape[1]
+        g = gate_up[:, :inter].float().clamp(max=limit)
+        u = gate_up[:, inter:].float().clamp(-limit, limit)
+        out.copy_((g * torch.sigmoid(alpha * g) * (u + 1.0)).to(out.dtype))
+
+    def route(self, logits, correction, groups, keep, top, weight_scale, chosen, weights, softmax_top=False):
+        if groups != 1 or not softmax_top:
+            raise NotImplementedError("the stand-in routes by the largest logits only")
+        z = logits if correction is None else logits + correction
+        order = torch.sort(z, dim=-1, descending=True, stable=True).indices[:, :top]
+        chosen.copy_(order.to(torch.int32))
+        weights.copy_(torch.softmax(torch.gather(logits, 1, order), -1) * weight_scale)
+
+    def group_rows(self, chosen, experts, group_off, tile_prefix, order, place):
+        pairs = chosen.numel()
+        self._entry_expert = chosen.reshape(-1).long().clone()
+        order.reshape(-1)[:pairs] = torch.arange(pairs, dtype=torch.int32)
+        place.reshape(-1)[:pairs] = torch.arange(pairs, dtype=torch.int32)
+
+    def grouped_linear(self, x, w, out, rows, x_group_cols=0, o_group_cols=0, lists=None, order_div=1, gather=True,
+                       sorted_x=None):
+        if lists is None:
+            raise NotImplementedError("the stand-in runs products over lists only")
+        order = lists[2].reshape(-1)
+        for i in range(rows):
+            src = x[int(order[i]) // order_div] if gather else x[i]
+            out[i] = (w[int(self._entry_expert[i])].float() @ src.float()).to(out.dtype)
+
+    def combine(self, x, d, y, place, weights, top, scale=None):
+        n = x.shape[0]
+        add = (weights[:, :, None] * y[place.reshape(-1).long()[:n * top]].view(n, top, -1)).sum(1)
+        if d is not None:
+            add = add + d
+        x += add if scale is None else scale * add
 
     def gla_scan(self, u, z, bias, tau, state, norm_w, eps, out, heads, dim, vdim, q_scale, ctx, tiles, scratch=None):
         t_seq, t_row0, t_rows, count = tiles

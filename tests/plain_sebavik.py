@@ -1,0 +1,167 @@
+"""The Sebavik design in float64 on the CPU: one function per mechanism, whole sequences, no cache.
+
+Slow and plain on purpose: it shares no code with the package and is what the package's kernels,
+cache and step function are compared with.  ``cfg`` is the dictionary of config.json, ``w`` maps
+tensor names to float64 (integer tables: int) numpy arrays.
+
+Notation: a sequence has T tokens at positions 0 .. T - 1; rows of an array are positions.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+
+def gelu_tanh(z):
+    return 0.5 * z * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+
+
+def sigmoid(z):
+    return 1.0 / (1.0 + np.exp(-z))
+
+
+def rms_unit(x, eps):
+    """Every row divided by sqrt(mean(row^2) + eps)."""
+    return x / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps)
+
+
+def rms_norm(x, weight, eps):
+    return rms_unit(x, eps) * weight
+
+
+def embed_tokens(cfg, w, tokens):
+    """Token rows times the scale, plus the bigram table's row of (previous token, token)."""
+    e = cfg["embedding"]
+    x = w["embed"][tokens] * e.get("scale", 1.0)
+    b = e.get("bigram")
+    if b:
+        rows = []
+        for t, tok in enumerate(tokens):
+            rows.append(b["buckets"] if t == 0 else (tokens[t - 1] * b["mul_prev"] + tok * b["mul_cur"]) % b["buckets"])
+        x = x + w["bigram"][rows]
+    return x
+
+
+def time_conv(h, taps_w):
+    """h + conv(h), conv(h)_t = sum_j taps_w[:, j] h_(t - taps + 1 + j), zeros before position 0."""
+    T = h.shape[0]
+    taps = taps_w.shape[1]
+    out = h.copy()
+    for t in range(T):
+        for j in range(taps):
+            s = t - taps + 1 + j
+            if s >= 0:
+                out[t] += taps_w[:, j] * h[s]
+    return out
+
+
+def attention(m, w, p, h, v_first, first_mixing):
+    """One attention mixer over the rows ``h``.  Returns (output, the values as cached)."""
+    T = h.shape[0]
+    H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    q = h @ w[p + ".q"].T + w[p + ".q.b"]
+    k = h @ w[p + ".k"].T + w[p + ".k.b"]
+    v = h @ w[p + ".v"].T + w[p + ".v.b"]
+    if m.get("v_mix") and not first_mixing:
+        lam = float(w[p + ".vmix"])
+        v = (1.0 - lam) * v + lam * v_first
+    q = q.reshape(T, H, D)
+    k = k.reshape(T, G, D)
+    vv = v.reshape(T, G, V)
+    cap = m.get("softcap")
+    mask = m.get("mask") or {}
+    size, keep = mask.get("size"), mask.get("keep_first", 0)
+    out = np.zeros((T, H, V))
+    for hd in range(H):
+        g = hd // (H // G)
+        r1, r2, sink = float(w[p + ".r1"][hd]), float(w[p + ".r2"][hd]), float(w[p + ".sink"][hd])
+        for i in range(T):
+            js = [j for j in range(i + 1) if size is None or i - j < size or j < keep]
+            s = np.array([q[i, hd] @ k[j, g] for j in js]) * m["scale"]
+            if cap:
+                s = cap * np.tanh(s / cap)
+            s = s - r1 * np.log1p(r2 * (i - np.array(js, dtype=np.float64)))
+            top = max(s.max(), sink)
+            e = np.exp(s - top)
+            den = e.sum() + math.exp(sink - top)
+            out[i, hd] = (e / den) @ vv[js, g]
+    return out.reshape(T, H * V) @ w[p + ".o"].T, v
+
+
+def dense_ff(mlp, w, p, h):
+    limit = mlp["limit"]
+    g = np.minimum(h @ w[p + ".gate"].T, limit)
+    u = np.clip(h @ w[p + ".up"].T, -limit, limit)
+    return (g * sigmoid(1.702 * g) * (u + 1.0)) @ w[p + ".down"].T
+
+
+def route(z, top):
+    """Per row: the ``top`` largest logits (the lower index on a tie) and the softmax over them."""
+    chosen = np.zeros((z.shape[0], top), dtype=np.int64)
+    weights = np.zeros((z.shape[0], top))
+    for t in range(z.shape[0]):
+        order = sorted(range(z.shape[1]), key=lambda e: (-z[t, e], e))[:top]
+        zz = z[t, order]
+        e = np.exp(zz - zz.max())
+        chosen[t], weights[t] = order, e / e.sum()
+    return chosen, weights
+
+
+def moe_ff(mlp, w, p, h):
+    top = mlp["router"]["top"]
+    chosen, weights = route(h @ w[p + ".router"].T, top)
+    out = np.zeros((h.shape[0], w[p + ".e0.down"].shape[0]))
+    for t in range(h.shape[0]):
+        for e, wt in zip(chosen[t], weights[t]):
+            q = f"{p}.e{e}"
+            a = w[q + ".gate"] @ h[t]
+            y = (a * sigmoid(a)) * (w[q + ".up"] @ h[t])
+            out[t] += wt * (w[q + ".down"] @ y)
+    return out
+
+
+def token_side(cfg, w, layer, tokens, x):
+    """The per-layer token input: what is added to the stream (before the residual factor)."""
+    dim = cfg["token_side"]["dim"]
+    p = f"l{layer}.side"
+    e = w["side.embed"][tokens][:, layer * dim:(layer + 1) * dim]
+    g = gelu_tanh(x @ w[p + ".gate"].T) * e
+    y = g @ w[p + ".proj"].T
+    return rms_unit(y, cfg["norm"]["eps"]) * w[p + ".norm"]
+
+
+def forward(cfg, w, tokens, collect=None):
+    """Logits [T, vocab] of one sequence.  ``collect``: a list that receives the stream after every layer."""
+    tokens = list(tokens)
+    eps = cfg["norm"]["eps"]
+    mult = cfg.get("residual_mult", 1.0)
+    canon = cfg.get("canon")
+    x = embed_tokens(cfg, w, tokens)
+    history = [x]
+    v_first = None
+    for i, layer in enumerate(cfg["layers"]):
+        p = f"l{i}"
+        h = rms_norm(x, w[p + ".norm1"], eps)
+        if canon:
+            h = time_conv(h, w[p + ".canon1"])
+        m = layer["mixer"]
+        y, v = attention(m, w, p + ".mix", h, v_first, v_first is None)
+        if m.get("v_mix") and v_first is None:
+            v_first = v
+        x = x + mult * (y * w[p + ".ls1"])
+        if layer.get("mlp"):
+            h = rms_norm(x, w[p + ".norm2"], eps)
+            if canon:
+                h = time_conv(h, w[p + ".canon2"])
+            mlp = layer["mlp"]
+            y = dense_ff(mlp, w, p + ".mlp", h) if mlp["kind"] == "dense" else moe_ff(mlp, w, p + ".mlp", h)
+            x = x + mult * (y * w[p + ".ls2"])
+        if cfg.get("token_side"):
+            x = x + mult * token_side(cfg, w, i, tokens, x)
+        history.append(x)
+        x = sum(float(w[p + ".dwa"][j]) * history[j] for j in range(i + 2))
+        if collect is not None:
+            collect.append(x)
+    x = rms_norm(x, w["final.norm"], eps)
+    return x @ w["embed"].T

@@ -35,10 +35,14 @@ class DecoderModel:
     def __init__(self, config, embedding: TokenEmbedding, blocks: Sequence, head: OutputHead,
                  schedule: Optional[Sequence[LayerRun]] = None,
                  position_encodings: Sequence[PositionEncoding] = (),
-                 block_prefix: str = "model.layers.{}", embed_prefix: str = "model", shared_parts: Sequence = ()):
+                 block_prefix: str = "model.layers.{}", embed_prefix: str = "model", shared_parts: Sequence = (),
+                 ignorable=None):
         """``shared_parts``: parts with weights that several blocks use (a table that every layer reads a
-        slice of); their tensors are declared and loaded once, with ``embed_prefix``."""
+        slice of); their tensors are declared and loaded once, with ``embed_prefix``.  ``ignorable``: a
+        predicate on names of stored tensors that this model has no use for (tensors of a sublayer that a
+        layer's configuration leaves out)."""
         self.config = config
+        self._ignorable = ignorable
         self.embedding = embedding
         self.blocks = list(blocks)
         self.head = head
@@ -118,7 +122,7 @@ class DecoderModel:
     def ignorable_tensor(self, name: str) -> bool:
         """Stored tensors that the model has no use for: the rotary tables that older exports
         keep as buffers (the engine builds its own from the configuration)."""
-        return name.endswith(".rotary_emb.inv_freq")
+        return name.endswith(".rotary_emb.inv_freq") or (self._ignorable is not None and bool(self._ignorable(name)))
 
     def tensor_aliases(self) -> Dict[str, str]:
         """Stored name -> declared tensor it must repeat: a tied head stored a second time."""

@@ -73,8 +73,16 @@ def build_sebavik(config: SebavikConfig) -> DecoderModel:
                                pair_table="bigram" if b is not None else None, pair_buckets=b.buckets if b else 0,
                                pair_mul_prev=b.mul_prev if b else 0, pair_mul_cur=b.mul_cur if b else 0)
     head = OutputHead(c.vocab, c.width, RMSNorm(c.width, c.eps, suffix=""), tied_to=embedding, norm_name="final.norm")
+    # a checkpoint may carry the tensors of what a layer's configuration leaves out: the norm, scale and
+    # convolution of an absent feed-forward, the mixing factor of a layer that does not mix its values
+    unused = set()
+    for i, layer in enumerate(c.layers):
+        if layer.mlp is None:
+            unused.update(f"l{i}.{BLOCK_NAMES[k]}" for k in ("ffn_norm", "scale_2", "conv_2"))
+        if not layer.mixer.v_mix:
+            unused.add(f"l{i}.{BLOCK_NAMES['mixer']}.{ScoredAttention.NAMES['vmix']}")
     return DecoderModel(c, embedding, blocks, head, schedule=schedule, block_prefix="l{}", embed_prefix="",
-                        shared_parts=[table] if table is not None else [])
+                        shared_parts=[table] if table is not None else [], ignorable=unused.__contains__)
 
 
 register_architecture("Sebavik", SebavikConfig.from_json, build_sebavik)

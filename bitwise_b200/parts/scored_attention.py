@@ -130,7 +130,7 @@ class ScoredAttention(Mixer):
             if self.qk_norm and normed:
                 specs.append(ParamSpec(f"{prefix}.{name}{n['norm']}", (size,), KEEP32, init="ones"))
         if self.value_mix:  # (the first such layer has the tensor too and no use for it)
-            specs.append(ParamSpec(f"{prefix}.{n['vmix']}", (), KEEP32))
+            specs.append(ParamSpec(f"{prefix}.{n['vmix']}", (), KEEP32, optional=self.value_mix == "source"))
         if self.distance_log:
             specs += [ParamSpec(f"{prefix}.{n['dist_a']}", (self.heads,), KEEP32),
                       ParamSpec(f"{prefix}.{n['dist_b']}", (self.heads,), KEEP32, init="positive")]

@@ -36,11 +36,13 @@ def embed_tokens(cfg, w, tokens):
     x = w["embed"][tokens] * e.get("scale", 1.0)
     b = e.get("bigram")
     if b:
-        rows = []
-        for t, tok in enumerate(tokens):
-            rows.append(b["buckets"] if t == 0 else (tokens[t - 1] * b["mul_prev"] + tok * b["mul_cur"]) % b["buckets"])
-        x = x + w["bigram"][rows]
+        x = x + w["bigram"][pair_rows(tokens, b["buckets"], b["mul_prev"], b["mul_cur"])]
     return x
+
+
+def pair_rows(tokens, buckets, mul_prev, mul_cur):
+    """The second table's row per position: a hash of the previous and the current token, the last row at position 0."""
+    return [buckets if t == 0 else (tokens[t - 1] * mul_prev + tok * mul_cur) % buckets for t, tok in enumerate(tokens)]
 
 
 def time_conv(h, taps_w):
@@ -56,6 +58,38 @@ def time_conv(h, taps_w):
     return out
 
 
+def visible(i, j, size, keep):
+    """Whether position i sees position j: not later, and inside the window or among the kept first ones."""
+    return j <= i and (size is None or i - j < size or j < keep)
+
+
+def windowed_sink_attention(q, k, v, scale, cap, r1, r2, sink, size, keep):
+    """q [T, H, D], k [T, G, D], v [T, G, V]; r1, r2, sink [H].  Returns [T, H, V].
+
+    score(i, j) = cap * tanh(q_i . k_j * scale / cap) - r1 * ln(1 + r2 * (i - j)) over the visible j; the
+    softmax's denominator holds exp(sink) besides, which has no value."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    out = np.zeros((T, H, v.shape[2]))
+    for hd in range(H):
+        g = hd // (H // G)
+        for i in range(T):
+            js = [j for j in range(i + 1) if visible(i, j, size, keep)]
+            s = np.array([q[i, hd] @ k[j, g] for j in js]) * scale
+            if cap:
+                s = cap * np.tanh(s / cap)
+            s = s - r1[hd] * np.log1p(r2[hd] * (i - np.array(js, dtype=np.float64)))
+            top = max(s.max(), sink[hd])
+            e = np.exp(s - top)
+            den = e.sum() + math.exp(sink[hd] - top)
+            out[i, hd] = (e / den) @ v[js, g]
+    return out
+
+
+def mix_values(v, v_first, lam):
+    return (1.0 - lam) * v + lam * v_first
+
+
 def attention(m, w, p, h, v_first, first_mixing):
     """One attention mixer over the rows ``h``.  Returns (output, the values as cached)."""
     T = h.shape[0]
@@ -64,28 +98,10 @@ def attention(m, w, p, h, v_first, first_mixing):
     k = h @ w[p + ".k"].T + w[p + ".k.b"]
     v = h @ w[p + ".v"].T + w[p + ".v.b"]
     if m.get("v_mix") and not first_mixing:
-        lam = float(w[p + ".vmix"])
-        v = (1.0 - lam) * v + lam * v_first
-    q = q.reshape(T, H, D)
-    k = k.reshape(T, G, D)
-    vv = v.reshape(T, G, V)
-    cap = m.get("softcap")
+        v = mix_values(v, v_first, float(w[p + ".vmix"]))
     mask = m.get("mask") or {}
-    size, keep = mask.get("size"), mask.get("keep_first", 0)
-    out = np.zeros((T, H, V))
-    for hd in range(H):
-        g = hd // (H // G)
-        r1, r2, sink = float(w[p + ".r1"][hd]), float(w[p + ".r2"][hd]), float(w[p + ".sink"][hd])
-        for i in range(T):
-            js = [j for j in range(i + 1) if size is None or i - j < size or j < keep]
-            s = np.array([q[i, hd] @ k[j, g] for j in js]) * m["scale"]
-            if cap:
-                s = cap * np.tanh(s / cap)
-            s = s - r1 * np.log1p(r2 * (i - np.array(js, dtype=np.float64)))
-            top = max(s.max(), sink)
-            e = np.exp(s - top)
-            den = e.sum() + math.exp(sink - top)
-            out[i, hd] = (e / den) @ vv[js, g]
+    out = windowed_sink_attention(q.reshape(T, H, D), k.reshape(T, G, D), v.reshape(T, G, V), m["scale"], m.get("softcap"),
+                                  w[p + ".r1"], w[p + ".r2"], w[p + ".sink"], mask.get("size"), mask.get("keep_first", 0))
     return out.reshape(T, H * V) @ w[p + ".o"].T, v
 
 
@@ -131,6 +147,11 @@ def token_side(cfg, w, layer, tokens, x):
     return rms_unit(y, cfg["norm"]["eps"]) * w[p + ".norm"]
 
 
+def depth_average(history, a):
+    """sum_j a[j] * history[j] over everything so far: the embedding's output and every layer's result."""
+    return sum(float(a[j]) * history[j] for j in range(len(history)))
+
+
 def forward(cfg, w, tokens, collect=None):
     """Logits [T, vocab] of one sequence.  ``collect``: a list that receives the stream after every layer."""
     tokens = list(tokens)
@@ -160,7 +181,7 @@ def forward(cfg, w, tokens, collect=None):
         if cfg.get("token_side"):
             x = x + mult * token_side(cfg, w, i, tokens, x)
         history.append(x)
-        x = sum(float(w[p + ".dwa"][j]) * history[j] for j in range(i + 2))
+        x = depth_average(history, w[p + ".dwa"])
         if collect is not None:
             collect.append(x)
     x = rms_norm(x, w["final.norm"], eps)

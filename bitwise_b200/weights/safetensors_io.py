@@ -122,7 +122,7 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]],
         if t.dtype not in _NAMES:
             raise SafetensorsError(f"cannot store tensor {name} of dtype {t.dtype}")
         t = t.detach().contiguous().cpu()
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                         "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)

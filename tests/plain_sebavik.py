@@ -13,6 +13,29 @@ import math
 import numpy as np
 
 
+# What a serving precision stores between two matrix products is rounded to it; the plain implementation rounds
+# nothing unless a test asks for it, to learn how large an error rounding alone causes for given weights:
+# ``with rounding(fn): forward(...)`` applies ``fn`` to what every matrix product reads besides the stream (the
+# normed input of a sublayer, queries, keys, values, the weighted values, the activated inner rows) and to
+# nothing that the design keeps in 32-bit (norms, scores, weights of the softmax, routers, the stream).
+_stored = [lambda a: a]
+
+
+class rounding:
+    def __init__(self, fn):
+        self.fn = fn
+
+    def __enter__(self):
+        _stored.append(self.fn)
+
+    def __exit__(self, *exc):
+        _stored.pop()
+
+
+def stored(a):
+    return _stored[-1](a)
+
+
 def gelu_tanh(z):
     return 0.5 * z * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
 
@@ -75,7 +98,7 @@ def windowed_sink_attention(q, k, v, scale, cap, r1, r2, sink, size, keep):
         g = hd // (H // G)
         for i in range(T):
             js = [j for j in range(i + 1) if visible(i, j, size, keep)]
-            s = np.array([q[i, hd] @ k[j, g] for j in js]) * scale
+            s = (k[js, g] @ q[i, hd]) * scale
             if cap:
                 s = cap * np.tanh(s / cap)
             s = s - r1[hd] * np.log1p(r2[hd] * (i - np.array(js, dtype=np.float64)))
@@ -100,16 +123,17 @@ def attention(m, w, p, h, v_first, first_mixing):
     if m.get("v_mix") and not first_mixing:
         v = mix_values(v, v_first, float(w[p + ".vmix"]))
     mask = m.get("mask") or {}
-    out = windowed_sink_attention(q.reshape(T, H, D), k.reshape(T, G, D), v.reshape(T, G, V), m["scale"], m.get("softcap"),
-                                  w[p + ".r1"], w[p + ".r2"], w[p + ".sink"], mask.get("size"), mask.get("keep_first", 0))
-    return out.reshape(T, H * V) @ w[p + ".o"].T, v
+    out = windowed_sink_attention(stored(q).reshape(T, H, D), stored(k).reshape(T, G, D), stored(v).reshape(T, G, V), m["scale"],
+                                  m.get("softcap"), w[p + ".r1"], w[p + ".r2"], w[p + ".sink"], mask.get("size"),
+                                  mask.get("keep_first", 0))
+    return stored(out.reshape(T, H * V)) @ w[p + ".o"].T, v
 
 
 def dense_ff(mlp, w, p, h):
     limit = mlp["limit"]
-    g = np.minimum(h @ w[p + ".gate"].T, limit)
-    u = np.clip(h @ w[p + ".up"].T, -limit, limit)
-    return (g * sigmoid(1.702 * g) * (u + 1.0)) @ w[p + ".down"].T
+    g = np.minimum(stored(h @ w[p + ".gate"].T), limit)
+    u = np.clip(stored(h @ w[p + ".up"].T), -limit, limit)
+    return stored(g * sigmoid(1.702 * g) * (u + 1.0)) @ w[p + ".down"].T
 
 
 def route(z, top):
@@ -131,8 +155,8 @@ def moe_ff(mlp, w, p, h):
     for t in range(h.shape[0]):
         for e, wt in zip(chosen[t], weights[t]):
             q = f"{p}.e{e}"
-            a = w[q + ".gate"] @ h[t]
-            y = (a * sigmoid(a)) * (w[q + ".up"] @ h[t])
+            a = stored(w[q + ".gate"] @ h[t])
+            y = stored((a * sigmoid(a)) * stored(w[q + ".up"] @ h[t]))
             out[t] += wt * (w[q + ".down"] @ y)
     return out
 
@@ -142,7 +166,7 @@ def token_side(cfg, w, layer, tokens, x):
     dim = cfg["token_side"]["dim"]
     p = f"l{layer}.side"
     e = w["side.embed"][tokens][:, layer * dim:(layer + 1) * dim]
-    g = gelu_tanh(x @ w[p + ".gate"].T) * e
+    g = stored(gelu_tanh(stored(x) @ w[p + ".gate"].T) * e)
     y = g @ w[p + ".proj"].T
     return rms_unit(y, cfg["norm"]["eps"]) * w[p + ".norm"]
 
@@ -166,6 +190,7 @@ def forward(cfg, w, tokens, collect=None):
         h = rms_norm(x, w[p + ".norm1"], eps)
         if canon:
             h = time_conv(h, w[p + ".canon1"])
+        h = stored(h)
         m = layer["mixer"]
         y, v = attention(m, w, p + ".mix", h, v_first, v_first is None)
         if m.get("v_mix") and v_first is None:
@@ -175,6 +200,7 @@ def forward(cfg, w, tokens, collect=None):
             h = rms_norm(x, w[p + ".norm2"], eps)
             if canon:
                 h = time_conv(h, w[p + ".canon2"])
+            h = stored(h)
             mlp = layer["mlp"]
             y = dense_ff(mlp, w, p + ".mlp", h) if mlp["kind"] == "dense" else moe_ff(mlp, w, p + ".mlp", h)
             x = x + mult * (y * w[p + ".ls2"])
@@ -184,5 +210,5 @@ def forward(cfg, w, tokens, collect=None):
         x = depth_average(history, w[p + ".dwa"])
         if collect is not None:
             collect.append(x)
-    x = rms_norm(x, w["final.norm"], eps)
+    x = stored(rms_norm(x, w["final.norm"], eps))
     return x @ w["embed"].T

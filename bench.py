@@ -684,6 +684,202 @@ def compare_favudra(args, pk):
     return line
 
 
+# ---- the Sebavik design beside Favudra at equal size (--compare sebavik) ------------------------
+SEBAVIK_SIZES = {
+    # width, layers, heads, kv_heads, dim = vdim, dense ff, window with kept first keys, taps, experts x top x ff,
+    # second table's buckets, token input's size, vocab
+    "small": dict(width=1024, layers=4, heads=8, kv_heads=2, dim=128, ff=2816, window=512, keep_first=4, taps=4,
+                  experts=8, top=2, expert_ff=1408, buckets=65521, side_dim=32, vocab=32768),
+    "medium": dict(width=2048, layers=4, heads=16, kv_heads=4, dim=128, ff=5632, window=1024, keep_first=16, taps=4,
+                   experts=16, top=4, expert_ff=1408, buckets=131071, side_dim=64, vocab=32768),
+}
+
+
+def sebavik_config(z):
+    """Layers alternate a dense and a routed feed-forward (the routed one multiplies a token with as many inner
+    columns as the dense one: top x expert ff = ff); every layer's attention has the window, the cap, the distance
+    term and the sink, and all but the first mix their values with the first layer's."""
+    from bitwise_b200.config.sebavik import BigramConfig, SebavikConfig, SebavikLayerConfig, SebavikMixerConfig, SebavikMlpConfig
+    layers = []
+    for i in range(z["layers"]):
+        m = SebavikMixerConfig(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5,
+                               softcap=30.0, window=z["window"], keep_first=z["keep_first"], v_mix=True)
+        mlp = SebavikMlpConfig("dense", z["ff"], 7.0) if i % 2 == 0 else SebavikMlpConfig("moe", z["expert_ff"], None,
+                                                                                          z["experts"], z["top"])
+        layers.append(SebavikLayerConfig(m, mlp))
+    return SebavikConfig(vocab=z["vocab"], width=z["width"], eps=1e-5, residual_mult=0.5, embedding_scale=z["width"] ** 0.5,
+                         layers=tuple(layers), bigram=BigramConfig(z["buckets"], 31, 17), canon_taps=z["taps"],
+                         side_dim=z["side_dim"])
+
+
+def sebavik_twin(z):
+    """Favudra with the same width, layers, heads, key/value heads, head size, feed-forward and vocabulary, its
+    layers alternating capped attention with a sink (and the convolution on q, k, v) and window attention."""
+    from bitwise_b200.config import FavudraConfig, FavudraLayerConfig, FavudraMixerConfig
+    layers = []
+    for i in range(z["layers"]):
+        if i % 2 == 0:
+            m = FavudraMixerConfig("attention", z["heads"], z["dim"], z["dim"], kv_heads=z["kv_heads"], scale=z["dim"] ** -0.5,
+                                   conv=z["taps"], rot_base=1e6, rot_dims=64, softcap=30.0)
+        else:
+            m = FavudraMixerConfig("attention_2", z["heads"], z["dim"], z["dim"], kv_heads=z["kv_heads"],
+                                   scale=z["dim"] ** -0.5, window=z["window"])
+        layers.append(FavudraLayerConfig(m, z["ff"]))
+    return FavudraConfig(vocab=z["vocab"], width=z["width"], eps=1e-5, embedding_scale=z["width"] ** 0.5, logit_scale=0.25,
+                         layers=tuple(layers))
+
+
+def sebavik_kernel_table(z, pk, page=16):
+    """Every kernel that the design adds or extends, alone at the size's shapes, beside the like kernel of the twin:
+    milliseconds and the fraction of its roofline (measured copy bandwidth or bf16 peak)."""
+    import torch
+    from bitwise_b200.kernels.ops import get_ops
+    from bitwise_b200.parts.rope import RotaryEncoding
+    from bitwise_b200.parts.scored_attention import SEQUENCE_TILE, distance_slopes
+    ops = get_ops("bfloat16")
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    H, G, hd, width, win, keep, taps = z["heads"], z["kv_heads"], z["dim"], z["width"], z["window"], z["keep_first"], z["taps"]
+    L, sd, vocab = z["layers"], z["side_dim"], z["vocab"]
+    out = {}
+
+    def frac_flops(flops, ms):
+        return round(flops / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 4)
+
+    def frac_bytes(nbytes, ms):
+        return round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+
+    def put(name, ms, frac, twin_ms, twin_frac, bound, twin):
+        out[name] = {"ms": round(ms, 4), "frac": frac, "twin_ms": round(twin_ms, 4), "twin_frac": twin_frac, "bound": bound,
+                     "twin": twin, "gap_ratio": round(twin_frac / frac, 2) if frac else None}
+
+    cos, sin = RotaryEncoding(64, 1e6, positions=2048).rotary_tables(dev)
+    slopes = torch.tensor(distance_slopes(H), dtype=torch.float32, device=dev)
+    r1 = torch.full((H,), 0.3, device=dev)
+    r2 = torch.full((H,), 0.5, device=dev)
+    sinks = torch.zeros(H, device=dev)
+    for label, seqs in (("prefill_2048", [(0, 2048)]), ("decode_b8_ctx2048", [(2047, 1)] * 8)):
+        keys = max(p0 + c for p0, c in seqs)
+        blocks = (keys + page - 1) // page
+        nseq = len(seqs)
+        table = torch.arange(nseq * blocks, dtype=torch.int32, device=dev).reshape(nseq, blocks)
+        heights = set(ops.scored_attention_tile_heights(H // G, hd, hd)) | {SEQUENCE_TILE}
+        b = KernelBatch(seqs, sorted(heights), dev)
+        b.seq_slot = torch.arange(nseq, dtype=torch.int32, device=dev)
+        b.tokens = torch.randint(0, vocab, (b.n,), dtype=torch.int32, device=dev)
+        n = b.n
+        prefill = n > nseq
+        seen = lambda p: min(p + 1, win) + max(0, min(keep, p + 1 - win))
+        wpairs = sum(sum(seen(p) for p in range(p0, p0 + c)) for p0, c in seqs)
+        kc = torch.randn(nseq * blocks + 1, G, page, hd, device=dev).to(bf)
+        vc = torch.randn(nseq * blocks + 1, G, page, hd, device=dev).to(bf)
+        q = torch.randn(n, H * hd, device=dev).to(bf)
+        o = torch.empty(n, H * hd, dtype=bf, device=dev)
+        # window attention with kept first keys, cap, logarithmic distance term and learned sink, beside the twin's
+        # window attention with distance slopes (whose values are its keys)
+        ms = timed_device(lambda: ops.scored_attention(q, kc, vc, table, o, H, G, hd, hd, hd ** -0.5, 30.0, True, None, win, b,
+                                                       dist_a=r1, dist_b=r2, sinks=sinks, keep_first=keep), flush=flush)
+        tms = timed_device(lambda: ops.scored_attention(q, kc, None, table, o, H, G, hd, hd, hd ** -0.5, 0.0, False, slopes, win, b),
+                           flush=flush)
+        if prefill:
+            put(f"attention_{label}", ms, frac_flops(4.0 * H * hd * wpairs, ms), tms, frac_flops(4.0 * H * hd * wpairs, tms),
+                "bf16 peak", "window attention with slopes")
+        else:
+            put(f"attention_{label}", ms, frac_bytes(nseq * seen(keys - 1) * 2 * G * hd * 2, ms), tms,
+                frac_bytes(nseq * min(keys, win) * G * hd * 2, tms), "copy bandwidth", "window attention with slopes")
+        # biases, mixed values and the way into the pages, beside the twin's convolution, norm, rotation and store
+        cols = (H + 2 * G) * hd
+        u = torch.randn(n, cols, device=dev)
+        bias = torch.randn(cols, device=dev)
+        first = torch.randn(n, G * hd, device=dev)
+        lam = torch.full((1,), 0.3, device=dev)
+        cw = torch.randn(cols, taps, device=dev)
+        st = torch.zeros(nseq + 1, taps - 1, cols, device=dev)
+        nw = torch.ones(hd, device=dev)
+        cwt = cw.t().contiguous()
+        ms = timed_device(lambda: ops.qkv_prepare(u, None, None, None, None, 1e-5, None, None, b, table, kc, vc, q, H, G, hd, hd,
+                                                  bias=bias, vmix_src=first, vmix_lambda=lam), flush=flush)
+        tms = timed_device(lambda: (ops.qkv_prepare(u, cw, st, nw, nw, 1e-5, cos, sin, b, table, kc, vc, q, H, G, hd, hd, conv_wt=cwt),
+                                    ops.conv_state_update(u, st, b, taps, b.query_tiles(SEQUENCE_TILE))), flush=flush)
+        put(f"bias_mix_store_{label}", ms, frac_bytes(n * (cols * 6 + G * hd * 4), ms), tms, frac_bytes(n * cols * 6, tms),
+            "copy bandwidth", "convolution, norm, rotation, store")
+        # the norm with the convolution over time (and the state's update), beside the twin's norm
+        stream = torch.randn(n, width, device=dev)
+        wn = torch.ones(width, device=dev)
+        taps_t = torch.randn(taps, width, device=dev)
+        cst = torch.zeros(nseq + 1, taps - 1, 2 * width, device=dev)
+        normed = torch.empty(n, 2 * width, device=dev)
+        a1 = torch.empty(n, width, dtype=bf, device=dev)
+        ms = timed_device(lambda: ops.norm_conv(stream, wn, 1e-5, taps_t, cst, 0, b, a1, normed, 0), flush=flush)
+        tms = timed_device(lambda: ops.rmsnorm(stream, wn, 1e-5, a1), flush=flush)
+        put(f"norm_conv_{label}", ms, frac_bytes(n * width * 10, ms), tms, frac_bytes(n * width * 6, tms), "copy bandwidth", "norm")
+        ms = timed_device(lambda: ops.conv_state_update(normed, cst, b, taps, b.query_tiles(SEQUENCE_TILE)), flush=flush)
+        out[f"conv_state_update_{label}"] = {"ms": round(ms, 4), "bound": "launch: taps - 1 rows per sequence"}
+        # the scaled sum of a sublayer's output, and the token input's norm with the depth average, beside the
+        # twin's norm after a sublayer
+        d = torch.randn(n, width, device=dev)
+        scale = torch.ones(width, device=dev)
+        history = torch.randn(n, (L + 1) * width, device=dev)
+        mix = torch.full((L + 1,), 0.2, device=dev)
+        tms = timed_device(lambda: ops.rmsnorm_residual(d, wn, 1e-5, stream), flush=flush)
+        ms = timed_device(lambda: ops.scaled_add(stream, scale, d, a1), flush=flush)
+        put(f"scaled_sum_{label}", ms, frac_bytes(n * width * 14, ms), tms, frac_bytes(n * width * 12, tms), "copy bandwidth",
+            "norm after a sublayer")
+        ms = timed_device(lambda: ops.normed_add_mix(stream, d, wn, 1e-5, 0.5, history, L, mix), flush=flush)
+        put(f"side_norm_depth_average_{label}", ms, frac_bytes(n * width * (16 + 4 * L), ms), tms, frac_bytes(n * width * 12, tms),
+            "copy bandwidth", "norm after a sublayer")
+        # the embedding with the second table, beside the twin's embedding
+        emb = torch.randn(vocab, width, device=dev).to(bf)
+        pair = torch.randn(z["buckets"] + 1, width, device=dev).to(bf)
+        last = torch.zeros(nseq + 1, 1, dtype=torch.int32, device=dev)
+        ms = timed_device(lambda: (ops.embed_pair(emb, pair, b, last, stream, 2.0, z["buckets"], 31, 17),
+                                   ops.last_token_update(b, last, b.query_tiles(SEQUENCE_TILE))), flush=flush)
+        tms = timed_device(lambda: ops.embed_rows(emb, b.tokens, stream, scale=2.0), flush=flush)
+        put(f"embedding_{label}", ms, frac_bytes(n * width * 8, ms), tms, frac_bytes(n * width * 6, tms), "copy bandwidth", "embedding")
+        # the token input's gate
+        t = torch.randn(n, sd, device=dev)
+        side = torch.randn(vocab, L * sd, device=dev).to(bf)
+        g = torch.empty(n, sd, dtype=bf, device=dev)
+        ms = timed_device(lambda: ops.token_gate(t, side, sd, b.tokens, g), flush=flush)
+        out[f"token_gate_{label}"] = {"ms": round(ms, 4), "frac": frac_bytes(n * sd * 8, ms), "bound": "copy bandwidth (launch at these sizes)"}
+        # the router: the softmax over the chosen logits beside the sigmoid scores of the routed design
+        E, top = z["experts"], z["top"]
+        logits = torch.randn(n, E, device=dev)
+        chosen = torch.empty(n, top, dtype=torch.int32, device=dev)
+        weights = torch.empty(n, top, device=dev)
+        ms = timed_device(lambda: ops.route(logits, None, 1, 1, top, 1.0, chosen, weights, softmax_top=True), flush=flush)
+        tms = timed_device(lambda: ops.route(logits, None, 1, 1, top, 1.0, chosen, weights), flush=flush)
+        put(f"route_{label}", ms, frac_bytes(n * (E * 4 + top * 8), ms), tms, frac_bytes(n * (E * 4 + top * 8), tms),
+            "copy bandwidth (launch at these sizes)", "sigmoid scores")
+        del kc, vc, emb, pair, side, history
+        torch.cuda.empty_cache()
+    return out
+
+
+def compare_sebavik(args, pk):
+    import torch
+    from bitwise_b200 import Model
+    z = SEBAVIK_SIZES[args.size]
+    ctx = args.ctx or 2048
+    line = {"metric": f"Sebavik beside Favudra at equal size ({args.size}): prefill of 2,048 tokens and decode at batch "
+                      f"{args.batch}, {ctx:,}-token contexts", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+            "data": "synthetic: random N(0,0.02) weights, prompt ids uniform over the vocabulary", "size": z,
+            "peaks": "of " + pk["source"], "l2": "whole models: weights and cache exceed L2; kernels alone: L2 flushed "
+            "before every repetition"}
+    for name, cfg in (("sebavik", sebavik_config(z)), ("favudra_twin", sebavik_twin(z))):
+        model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", fast=True)
+        with ClockSampler() as clocks:
+            ms, launches = run_decode(model, args.batch, ctx, args.steps, max(3, args.warmup), args.page)
+        pms = run_prefill(model, 2048, reps=5, warmup=3, page=args.page)
+        line[name] = {"decode_tok_s": round(args.batch / (ms / 1e3), 1), "decode_ms_per_step": round(ms, 4),
+                      "prefill_tok_s": round(2048 / (pms / 1e3), 1), "prefill_ms": round(pms, 3),
+                      "weight_bytes": model.weight_bytes, "gpu_launches": launches, "clocks": clocks.summary()}
+        del model
+        torch.cuda.empty_cache()
+    line["kernels"] = sebavik_kernel_table(z, pk, args.page)
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -702,9 +898,9 @@ def main():
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="only the headline decode (for profiling runs)")
     ap.add_argument("--skip-prefill", action="store_true")
-    ap.add_argument("--compare", default="", choices=["", "nuderax", "favudra"],
-                    help="instead of the headline: this design beside the Llama architecture at equal size")
-    ap.add_argument("--size", default="small", choices=sorted(set(NUDERAX_SIZES) | set(FAVUDRA_SIZES)),
+    ap.add_argument("--compare", default="", choices=["", "nuderax", "favudra", "sebavik"],
+                    help="instead of the headline: this design beside its closest earlier architecture at equal size")
+    ap.add_argument("--size", default="small", choices=sorted(set(NUDERAX_SIZES) | set(FAVUDRA_SIZES) | set(SEBAVIK_SIZES)),
                     help="layer sizes for --compare")
     args = ap.parse_args()
 
@@ -724,6 +920,9 @@ def main():
         return 0
     if args.compare == "favudra":
         print(json.dumps(compare_favudra(args, pk)))
+        return 0
+    if args.compare == "sebavik":
+        print(json.dumps(compare_sebavik(args, pk)))
         return 0
     title, full_layers, _, shape_ctx = SHAPES[args.shape]
     args.layers = args.layers or full_layers

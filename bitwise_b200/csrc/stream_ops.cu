@@ -6,7 +6,8 @@
 //   last_token_update the state slot's token after a step: the last token of each sequence
 //   norm_conv         h = rmsnorm(x) w, out = h + conv(h): a causal convolution over time on every
 //                     channel, conv(h)_t = sum_j c[:, j] h_(t - taps + 1 + j); rows before the step's
-//                     first come from the request's state slot, zeros before position 0
+//                     first come from the request's state slot, zeros before position 0; h is kept
+//                     for the rows that the state holds after the step
 //   scaled_add        x += s * d per channel (or nothing added), optionally also x in the activation type
 //   token_gate        g = gelu_tanh(t) * e[token], e a slice of a per-token table
 //   normed_add_mix    x += m * y / rms(y) * w (y optional), keep the row as entry `index` of the row's
@@ -58,51 +59,118 @@ __global__ void last_token_update_kernel(const int* __restrict__ tokens, const i
   last_token[seq_slot[tile_seq[t]]] = tokens[tile_row0[t] + tile_rows[t] - 1];
 }
 
-// One block per row. The normed rows of the taps before it are formed again from x (same arithmetic,
-// same bits as the row's own block forms) or read from the state slot.
+// A block takes `rows_per_block` consecutive rows of the step (at most kConvRows) and the channels [c0, c0 +
+// chans) of them. Its warps first form 1 / rms of those rows and of the taps - 1 rows before them that belong
+// to the first row's sequence, a row per warp at a time (the same arithmetic whichever block forms a row and
+// however the step is cut, so a row's normed values are the same bits as the row itself and as the rows after
+// it see them); then every thread walks its channels down the block's rows, with the normed values of the
+// taps - 1 rows before in registers. Rows before the step's first of a sequence come from the request's state
+// slot. `normed` is written only where `conv_state_update` reads it: the last taps - 1 rows of a sequence's
+// portion.
+constexpr int kConvRows = 8;
+
+int sm_count() {
+  static int sms = 0;
+  if (sms <= 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+template <int kTaps /* 0: any number up to kMaxTaps, rows before read again */>
 __global__ void __launch_bounds__(kThreads)
 norm_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, const float* __restrict__ taps_t,
-                 int taps, const float* __restrict__ state, int state_cols, int state_col0, const int* __restrict__ pos,
+                 int taps_any, const float* __restrict__ state, int state_cols, int state_col0, const int* __restrict__ pos,
                  const int* __restrict__ row_seq, const int* __restrict__ seq_row0, const int* __restrict__ seq_slot,
-                 act_t* __restrict__ out, float* __restrict__ normed, int normed_cols, int normed_col0, int width) {
+                 act_t* __restrict__ out, float* __restrict__ normed, int normed_cols, int normed_col0, int n, int width,
+                 int rows_per_block, int chans) {
   bw::pdl_enter();
-  __shared__ float red[32];
-  __shared__ float inv_of[kMaxTaps];
-  const int r = blockIdx.x;
-  const int p = pos[r];
-  const int seq = row_seq[r];
-  const int row0 = seq_row0[seq];
-  const size_t slot = static_cast<size_t>(seq_slot[seq]);
-  // 1 / rms of this row and of the rows of the step that the taps reach
-  for (int back = 0; back < taps; ++back) {
-    const int rr = r - back;
-    if (p - back < 0 || rr < row0) break;  // (uniform over the block)
+  const int taps = kTaps ? kTaps : taps_any;
+  __shared__ float inv_of[kConvRows + kMaxTaps];  // entry j: row r0 - (taps - 1) + j
+  __shared__ int row_pos[kConvRows], row_first[kConvRows], row_slot[kConvRows], row_keep[kConvRows];
+  const int r0 = blockIdx.x * rows_per_block;
+  const int rows = min(rows_per_block, n - r0);
+  const int first = r0 - (taps - 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq0 = row_seq[r0];
+  for (int j = warp; j < rows + taps - 1; j += kThreads / 32) {
+    const int rr = first + j;
+    if (rr < 0 || (rr < r0 && row_seq[rr] != seq0)) continue;  // (uniform over the warp)
     const float* xr = x + static_cast<size_t>(rr) * width;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < width; i += kThreads) ss = __fmaf_rn(xr[i], xr[i], ss);
-    const float inv = bw::rms_scale(bw::block_sum(ss, red), width, eps);
-    if (threadIdx.x == 0) inv_of[back] = inv;
+#pragma unroll 8
+    for (int i = lane; i < width; i += 32) ss = __fmaf_rn(xr[i], xr[i], ss);
+    ss = bw::warp_sum(ss);
+    if (lane == 0) inv_of[j] = bw::rms_scale(ss, width, eps);
+  }
+  if (threadIdx.x < rows) {
+    const int r = r0 + threadIdx.x;
+    const int seq = row_seq[r];
+    const int ahead = r + taps - 1;  // the row's place in the state after the step: among its sequence's last taps - 1
+    row_pos[threadIdx.x] = pos[r];
+    row_first[threadIdx.x] = seq_row0[seq];
+    row_slot[threadIdx.x] = seq_slot[seq];
+    row_keep[threadIdx.x] = taps > 1 && (ahead >= n || row_seq[ahead] != seq);
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < width; i += kThreads) {
+  const int c0 = blockIdx.y * chans;
+  const int c1 = min(width, c0 + chans);
+  for (int i = c0 + threadIdx.x; i < c1; i += kThreads) {
     const float wi = w[i];
-    const float own = bw::rms_apply(x[static_cast<size_t>(r) * width + i], inv_of[0], wi);
-    float acc = 0.0f;
-    for (int t = 0; t < taps; ++t) {  // taps ascending
-      const int back = taps - 1 - t;
-      if (p - back < 0) continue;
-      const int rr = r - back;
-      float h;
-      if (back == 0)
-        h = own;
-      else if (rr >= row0)
-        h = bw::rms_apply(x[static_cast<size_t>(rr) * width + i], inv_of[back], wi);
-      else
-        h = state[(slot * (taps - 1) + (taps - 1 - (row0 - rr))) * state_cols + state_col0 + i];
-      acc = __fmaf_rn(taps_t[static_cast<size_t>(t) * width + i], h, acc);
+    if constexpr (kTaps != 0) {
+      float c[kTaps], h[kTaps];  // h[t]: the normed value of row r - (kTaps - 1) + t, where the step has that row
+#pragma unroll
+      for (int t = 0; t < kTaps; ++t) c[t] = taps_t[static_cast<size_t>(t) * width + i];
+#pragma unroll
+      for (int t = 0; t + 1 < kTaps; ++t) {
+        const int rr = first + t;
+        h[t + 1] = rr >= row_first[0] ? bw::rms_apply(x[static_cast<size_t>(rr) * width + i], inv_of[t], wi) : 0.0f;
+      }
+      for (int j = 0; j < rows; ++j) {
+        const int r = r0 + j;
+        const int p = row_pos[j], row0 = row_first[j];
+#pragma unroll
+        for (int t = 0; t + 1 < kTaps; ++t) h[t] = h[t + 1];
+        h[kTaps - 1] = bw::rms_apply(x[static_cast<size_t>(r) * width + i], inv_of[j + kTaps - 1], wi);
+        float acc = 0.0f;
+#pragma unroll
+        for (int t = 0; t < kTaps; ++t) {  // taps ascending
+          const int back = kTaps - 1 - t;
+          if (p - back < 0) continue;
+          float hv = h[t];
+          if (r - back < row0)
+            hv = state[(static_cast<size_t>(row_slot[j]) * (kTaps - 1) + (kTaps - 1 - (row0 - (r - back)))) * state_cols +
+                       state_col0 + i];
+          acc = __fmaf_rn(c[t], hv, acc);
+        }
+        if (row_keep[j]) normed[static_cast<size_t>(r) * normed_cols + normed_col0 + i] = h[kTaps - 1];
+        out[static_cast<size_t>(r) * width + i] = bw::from_f<act_t>(__fadd_rn(h[kTaps - 1], acc));
+      }
+    } else {
+      for (int j = 0; j < rows; ++j) {
+        const int r = r0 + j;
+        const int p = row_pos[j], row0 = row_first[j];
+        const float own = bw::rms_apply(x[static_cast<size_t>(r) * width + i], inv_of[j + taps - 1], wi);
+        float acc = 0.0f;
+        for (int t = 0; t < taps; ++t) {  // taps ascending
+          const int back = taps - 1 - t;
+          if (p - back < 0) continue;
+          const int rr = r - back;
+          float hv;
+          if (back == 0)
+            hv = own;
+          else if (rr >= row0)
+            hv = bw::rms_apply(x[static_cast<size_t>(rr) * width + i], inv_of[j + t], wi);
+          else
+            hv = state[(static_cast<size_t>(row_slot[j]) * (taps - 1) + (taps - 1 - (row0 - rr))) * state_cols + state_col0 + i];
+          acc = __fmaf_rn(taps_t[static_cast<size_t>(t) * width + i], hv, acc);
+        }
+        if (row_keep[j]) normed[static_cast<size_t>(r) * normed_cols + normed_col0 + i] = own;
+        out[static_cast<size_t>(r) * width + i] = bw::from_f<act_t>(__fadd_rn(own, acc));
+      }
     }
-    normed[static_cast<size_t>(r) * normed_cols + normed_col0 + i] = own;
-    out[static_cast<size_t>(r) * width + i] = bw::from_f<act_t>(__fadd_rn(own, acc));
   }
 }
 
@@ -203,9 +271,24 @@ BW_API int BW_FN(norm_conv)(const float* x, const float* w, float eps, const flo
     bw::set_error("norm_conv: %d taps (1 .. %d, with the requests' state from 2 on)", taps, kMaxTaps);
     return -1;
   }
-  bw::launch_pdl(norm_conv_kernel, dim3(n), dim3(kThreads), 0, stream, x, w, eps, taps_t, taps, state, state_cols,
-                 state_col0, pos, row_seq, seq_row0, seq_slot, static_cast<act_t*>(out), normed, normed_cols, normed_col0,
-                 width);
+  // rows per block and channels per block: enough blocks to fill the device where the step has the work for it
+  const int rows_per_block = n >= kConvRows * 2 * sm_count() ? kConvRows : max(1, min(kConvRows, n / sm_count()));
+  const int groups = (n + rows_per_block - 1) / rows_per_block;
+  int slices = max(1, min((width + kThreads - 1) / kThreads, (2 * sm_count() + groups - 1) / groups));
+  const int chans = ((width + slices - 1) / slices + 31) / 32 * 32;
+  slices = (width + chans - 1) / chans;
+  auto go = [&](auto kernel) {
+    bw::launch_pdl(kernel, dim3(groups, slices), dim3(kThreads), 0, stream, x, w, eps, taps_t, taps, state, state_cols,
+                   state_col0, pos, row_seq, seq_row0, seq_slot, static_cast<act_t*>(out), normed, normed_cols, normed_col0, n,
+                   width, rows_per_block, chans);
+  };
+  switch (taps) {
+    case 1: go(norm_conv_kernel<1>); break;
+    case 2: go(norm_conv_kernel<2>); break;
+    case 3: go(norm_conv_kernel<3>); break;
+    case 4: go(norm_conv_kernel<4>); break;
+    default: go(norm_conv_kernel<0>); break;
+  }
   return bw::launch_status();
 }
 

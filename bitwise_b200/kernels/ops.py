@@ -1201,7 +1201,8 @@ class KernelOps:
         """h = rmsnorm(x) * weight; out = h + conv(h) with conv(h)_t = sum_j taps_t[j] * h_(t - taps + 1 + j) per channel
         (``taps_t`` float32 [taps, width]); rows before the step's first of a sequence are read from ``state``
         [slots, taps - 1, state columns] at columns state_col0 .., zeros before position 0.  ``normed`` (float32 [n,
-        columns], written at columns normed_col0 ..) receives h, for ``conv_state_update``."""
+        columns], written at columns normed_col0 ..) receives h of the last taps - 1 rows of every sequence's portion, which
+        is what ``conv_state_update`` reads; its other rows are left as they are."""
         n, width = out.shape
         _need(x, torch.float32, "norm_conv x", 2)
         _need(weight, torch.float32, "norm_conv weight", 1)

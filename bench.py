@@ -812,7 +812,7 @@ def sebavik_kernel_table(z, pk, page=16):
         a1 = torch.empty(n, width, dtype=bf, device=dev)
         ms = timed_device(lambda: ops.norm_conv(stream, wn, 1e-5, taps_t, cst, 0, b, a1, normed, 0), flush=flush)
         tms = timed_device(lambda: ops.rmsnorm(stream, wn, 1e-5, a1), flush=flush)
-        put(f"norm_conv_{label}", ms, frac_bytes(n * width * 10, ms), tms, frac_bytes(n * width * 6, tms), "copy bandwidth", "norm")
+        put(f"norm_conv_{label}", ms, frac_bytes(n * width * 6, ms), tms, frac_bytes(n * width * 6, tms), "copy bandwidth", "norm")
         ms = timed_device(lambda: ops.conv_state_update(normed, cst, b, taps, b.query_tiles(SEQUENCE_TILE)), flush=flush)
         out[f"conv_state_update_{label}"] = {"ms": round(ms, 4), "bound": "launch: taps - 1 rows per sequence"}
         # the scaled sum of a sublayer's output, and the token input's norm with the depth average, beside the

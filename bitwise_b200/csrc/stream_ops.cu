@@ -68,6 +68,7 @@ __global__ void last_token_update_kernel(const int* __restrict__ tokens, const i
 // slot. `normed` is written only where `conv_state_update` reads it: the last taps - 1 rows of a sequence's
 // portion.
 constexpr int kConvRows = 8;
+constexpr int kConvThreads = 512;  // one round of sums for eight rows and the rows before them
 
 int sm_count() {
   static int sms = 0;
@@ -79,8 +80,37 @@ int sm_count() {
   return sms;
 }
 
+// A lane's share of a row's sum of squares: the quads lane, lane + 32, ... of the row, one running sum per place
+// in the quad, then the tail. The order is the same with 16-byte loads and without, so the bits do not depend on
+// where the row lies.
+__device__ __forceinline__ float lane_sumsq(const float* __restrict__ xr, int width, int lane, bool vec) {
+  float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+  const int quads = width >> 2;
+  if (vec) {
+    const float4* x4 = reinterpret_cast<const float4*>(xr);
+#pragma unroll 8
+    for (int q = lane; q < quads; q += 32) {
+      const float4 v = x4[q];
+      a0 = __fmaf_rn(v.x, v.x, a0);
+      a1 = __fmaf_rn(v.y, v.y, a1);
+      a2 = __fmaf_rn(v.z, v.z, a2);
+      a3 = __fmaf_rn(v.w, v.w, a3);
+    }
+  } else {
+    for (int q = lane; q < quads; q += 32) {
+      const float* v = xr + 4 * q;
+      a0 = __fmaf_rn(v[0], v[0], a0);
+      a1 = __fmaf_rn(v[1], v[1], a1);
+      a2 = __fmaf_rn(v[2], v[2], a2);
+      a3 = __fmaf_rn(v[3], v[3], a3);
+    }
+  }
+  for (int i = (quads << 2) + lane; i < width; i += 32) a0 = __fmaf_rn(xr[i], xr[i], a0);
+  return __fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3));
+}
+
 template <int kTaps /* 0: any number up to kMaxTaps, rows before read again */>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kConvThreads, 2)
 norm_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, const float* __restrict__ taps_t,
                  int taps_any, const float* __restrict__ state, int state_cols, int state_col0, const int* __restrict__ pos,
                  const int* __restrict__ row_seq, const int* __restrict__ seq_row0, const int* __restrict__ seq_slot,
@@ -94,59 +124,89 @@ norm_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, float
   const int rows = min(rows_per_block, n - r0);
   const int first = r0 - (taps - 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq0 = row_seq[r0];
-  for (int j = warp; j < rows + taps - 1; j += kThreads / 32) {
-    const int rr = first + j;
-    if (rr < 0 || (rr < r0 && row_seq[rr] != seq0)) continue;  // (uniform over the warp)
-    const float* xr = x + static_cast<size_t>(rr) * width;
-    float ss = 0.0f;
-#pragma unroll 8
-    for (int i = lane; i < width; i += 32) ss = __fmaf_rn(xr[i], xr[i], ss);
-    ss = bw::warp_sum(ss);
-    if (lane == 0) inv_of[j] = bw::rms_scale(ss, width, eps);
-  }
-  if (threadIdx.x < rows) {
+  const bool vec = (width & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  // what the first threads look up about the block's rows is asked for before the sums, and what depends on the
+  // answers between the two rounds of sums, so that no lookup is waited for alone
+  const bool meta = threadIdx.x < rows;
+  int m_pos = 0, m_seq = 0, m_ahead = -1;
+  if (meta) {
     const int r = r0 + threadIdx.x;
-    const int seq = row_seq[r];
     const int ahead = r + taps - 1;  // the row's place in the state after the step: among its sequence's last taps - 1
-    row_pos[threadIdx.x] = pos[r];
-    row_first[threadIdx.x] = seq_row0[seq];
-    row_slot[threadIdx.x] = seq_slot[seq];
-    row_keep[threadIdx.x] = taps > 1 && (ahead >= n || row_seq[ahead] != seq);
+    m_pos = pos[r];
+    m_seq = row_seq[r];
+    if (ahead < n) m_ahead = row_seq[ahead];
+  }
+  const int seq0 = row_seq[r0];
+  for (int j = warp; j < rows; j += kConvThreads / 32) {  // the block's own rows
+    const float ss = bw::warp_sum(lane_sumsq(x + static_cast<size_t>(r0 + j) * width, width, lane, vec));
+    if (lane == 0) inv_of[taps - 1 + j] = bw::rms_scale(ss, width, eps);
+  }
+  int m_first = 0, m_slot = 0;
+  if (meta) {
+    m_first = seq_row0[m_seq];
+    m_slot = seq_slot[m_seq];
+  }
+  for (int t = warp; t < taps - 1; t += kConvThreads / 32) {  // the rows before them that the first row's sequence has
+    const int rr = first + t;
+    if (rr < 0 || row_seq[rr] != seq0) continue;  // (uniform over the warp)
+    const float ss = bw::warp_sum(lane_sumsq(x + static_cast<size_t>(rr) * width, width, lane, vec));
+    if (lane == 0) inv_of[t] = bw::rms_scale(ss, width, eps);
+  }
+  if (meta) {
+    row_pos[threadIdx.x] = m_pos;
+    row_first[threadIdx.x] = m_first;
+    row_slot[threadIdx.x] = m_slot;
+    // bit 0: the state keeps the row; bit 1: the step holds all taps - 1 rows before it
+    row_keep[threadIdx.x] = (taps > 1 && m_ahead != m_seq ? 1 : 0) |
+                            (m_pos >= taps - 1 && r0 + static_cast<int>(threadIdx.x) - (taps - 1) >= m_first ? 2 : 0);
   }
   __syncthreads();
   const int c0 = blockIdx.y * chans;
   const int c1 = min(width, c0 + chans);
-  for (int i = c0 + threadIdx.x; i < c1; i += kThreads) {
+  for (int i = c0 + threadIdx.x; i < c1; i += kConvThreads) {
     const float wi = w[i];
     if constexpr (kTaps != 0) {
-      float c[kTaps], h[kTaps];  // h[t]: the normed value of row r - (kTaps - 1) + t, where the step has that row
+      // the block's rows and the kTaps - 1 before them, loaded together: h[t] is the normed value of row first + t,
+      // where the step has that row for the first row's sequence (the rows of a later sequence all lie in the block)
+      float c[kTaps], h[kConvRows + kTaps - 1];
 #pragma unroll
       for (int t = 0; t < kTaps; ++t) c[t] = taps_t[static_cast<size_t>(t) * width + i];
 #pragma unroll
-      for (int t = 0; t + 1 < kTaps; ++t) {
+      for (int t = 0; t < kConvRows + kTaps - 1; ++t) {
         const int rr = first + t;
-        h[t + 1] = rr >= row_first[0] ? bw::rms_apply(x[static_cast<size_t>(rr) * width + i], inv_of[t], wi) : 0.0f;
+        const bool have = t < rows + kTaps - 1 && (t >= kTaps - 1 || rr >= row_first[0]);
+        h[t] = have ? x[static_cast<size_t>(rr) * width + i] : 0.0f;
       }
-      for (int j = 0; j < rows; ++j) {
-        const int r = r0 + j;
-        const int p = row_pos[j], row0 = row_first[j];
 #pragma unroll
-        for (int t = 0; t + 1 < kTaps; ++t) h[t] = h[t + 1];
-        h[kTaps - 1] = bw::rms_apply(x[static_cast<size_t>(r) * width + i], inv_of[j + kTaps - 1], wi);
-        float acc = 0.0f;
+      for (int t = 0; t < kConvRows + kTaps - 1; ++t) {
+        const bool have = t < rows + kTaps - 1 && (t >= kTaps - 1 || first + t >= row_first[0]);
+        if (have) h[t] = bw::rms_apply(h[t], inv_of[t], wi);
+      }
 #pragma unroll
-        for (int t = 0; t < kTaps; ++t) {  // taps ascending
-          const int back = kTaps - 1 - t;
-          if (p - back < 0) continue;
-          float hv = h[t];
-          if (r - back < row0)
-            hv = state[(static_cast<size_t>(row_slot[j]) * (kTaps - 1) + (kTaps - 1 - (row0 - (r - back)))) * state_cols +
-                       state_col0 + i];
-          acc = __fmaf_rn(c[t], hv, acc);
+      for (int j = 0; j < kConvRows; ++j) {
+        if (j < rows) {
+          const int r = r0 + j;
+          const int flags = row_keep[j];
+          float acc = 0.0f;
+          if (flags & 2) {
+#pragma unroll
+            for (int t = 0; t < kTaps; ++t) acc = __fmaf_rn(c[t], h[j + t], acc);  // taps ascending
+          } else {
+            const int p = row_pos[j], row0 = row_first[j];
+#pragma unroll
+            for (int t = 0; t < kTaps; ++t) {
+              const int back = kTaps - 1 - t;
+              if (p - back < 0) continue;
+              float hv = h[j + t];
+              if (r - back < row0)
+                hv = state[(static_cast<size_t>(row_slot[j]) * (kTaps - 1) + (kTaps - 1 - (row0 - (r - back)))) * state_cols +
+                           state_col0 + i];
+              acc = __fmaf_rn(c[t], hv, acc);
+            }
+          }
+          if (flags & 1) normed[static_cast<size_t>(r) * normed_cols + normed_col0 + i] = h[j + kTaps - 1];
+          out[static_cast<size_t>(r) * width + i] = bw::from_f<act_t>(__fadd_rn(h[j + kTaps - 1], acc));
         }
-        if (row_keep[j]) normed[static_cast<size_t>(r) * normed_cols + normed_col0 + i] = h[kTaps - 1];
-        out[static_cast<size_t>(r) * width + i] = bw::from_f<act_t>(__fadd_rn(h[kTaps - 1], acc));
       }
     } else {
       for (int j = 0; j < rows; ++j) {
@@ -167,7 +227,7 @@ norm_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, float
             hv = state[(static_cast<size_t>(row_slot[j]) * (taps - 1) + (taps - 1 - (row0 - rr))) * state_cols + state_col0 + i];
           acc = __fmaf_rn(taps_t[static_cast<size_t>(t) * width + i], hv, acc);
         }
-        if (row_keep[j]) normed[static_cast<size_t>(r) * normed_cols + normed_col0 + i] = own;
+        if (row_keep[j] & 1) normed[static_cast<size_t>(r) * normed_cols + normed_col0 + i] = own;
         out[static_cast<size_t>(r) * width + i] = bw::from_f<act_t>(__fadd_rn(own, acc));
       }
     }
@@ -274,11 +334,11 @@ BW_API int BW_FN(norm_conv)(const float* x, const float* w, float eps, const flo
   // rows per block and channels per block: enough blocks to fill the device where the step has the work for it
   const int rows_per_block = n >= kConvRows * 2 * sm_count() ? kConvRows : max(1, min(kConvRows, n / sm_count()));
   const int groups = (n + rows_per_block - 1) / rows_per_block;
-  int slices = max(1, min((width + kThreads - 1) / kThreads, (2 * sm_count() + groups - 1) / groups));
+  int slices = max(1, min((width + kConvThreads - 1) / kConvThreads, (sm_count() + groups - 1) / groups));
   const int chans = ((width + slices - 1) / slices + 31) / 32 * 32;
   slices = (width + chans - 1) / chans;
   auto go = [&](auto kernel) {
-    bw::launch_pdl(kernel, dim3(groups, slices), dim3(kThreads), 0, stream, x, w, eps, taps_t, taps, state, state_cols,
+    bw::launch_pdl(kernel, dim3(groups, slices), dim3(kConvThreads), 0, stream, x, w, eps, taps_t, taps, state, state_cols,
                    state_col0, pos, row_seq, seq_row0, seq_slot, static_cast<act_t*>(out), normed, normed_cols, normed_col0, n,
                    width, rows_per_block, chans);
   };

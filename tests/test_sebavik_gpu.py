@@ -176,6 +176,40 @@ def test_norm_and_convolution_over_time_with_state_across_steps(dtype, width, ta
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width,taps", [(260, 4), (258, 3), (72, 5), (1100, 2), (36, 1)])
+def test_norm_and_convolution_over_time_in_long_steps(dtype, width, taps):
+    """Steps of more than a thousand rows, where a block of the kernel takes several rows: sequences of one to 1,400
+    rows side by side, so that portions begin and end at every place of a block's rows, cut once in the middle (the
+    second step reads the state that the first one left in dirty slots)."""
+    ops = ops_of(dtype)
+    lengths, first = [1400, 3, 1, 905, 8, 2], [700, 2, 1, 500, 5, 1]
+    g = torch.Generator().manual_seed(width * taps)
+    xs = [torch.randn(L, width, generator=g) * 2 for L in lengths]
+    nw, cw = 1 + 0.3 * torch.randn(width, generator=g), 0.6 * torch.randn(width, taps, generator=g)
+    want = [P.time_conv(P.rms_norm(f64(x), f64(nw), 1e-5), f64(cw)) for x in xs]
+    state = torch.full((len(lengths) + 1, max(taps - 1, 1), width), 1e3, device=DEV) if taps > 1 else None
+    got = [np.zeros((L, width)) for L in lengths]
+    steps = [[(s, 0, f) for s, f in enumerate(first)],
+             [(s, f, L - f) for s, (L, f) in enumerate(zip(lengths, first)) if L > f]]
+    for step in steps:
+        b = Batch([(p0, n) for _, p0, n in step], slots=[len(lengths) - s for s, _, _ in step])
+        x = torch.cat([xs[s][p0:p0 + n] for s, p0, n in step]).to(DEV)
+        normed = torch.full((b.n, width), float("nan"), device=DEV)
+        out = torch.empty(b.n, width, dtype=act(dtype), device=DEV)
+        ops.norm_conv(x, nw.to(DEV), 1e-5, cw.t().contiguous().to(DEV), state, 0, b, out, normed, 0)
+        if taps > 1:
+            ops.conv_state_update(normed, state, b, taps, b.query_tiles(SEQ))
+        r = 0
+        for s, p0, n in step:
+            got[s][p0:p0 + n] = f64(out[r:r + n])
+            r += n
+    for s in range(len(lengths)):
+        close(got[s], want[s], dtype, f"sequence {s}")
+    if taps > 1:
+        assert torch.isfinite(state[1:]).all()                 # every slot's rows were written from rows that were kept
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("width,entries", [(50, 4), (256, 6), (1500, 2)])
 def test_scaled_sums_token_input_and_depth_average(dtype, width, entries):
     ops = ops_of(dtype)

@@ -708,7 +708,7 @@ def sebavik_config(z):
                                                                                           z["experts"], z["top"])
         layers.append(SebavikLayerConfig(m, mlp))
     return SebavikConfig(vocab=z["vocab"], width=z["width"], eps=1e-5, residual_mult=0.5, embedding_scale=z["width"] ** 0.5,
-                         layers=tuple(layers), bigram=BigramConfig(z["buckets"], 31, 17), canon_taps=z["taps"],
+                         layers=tuple(layers), bigram=BigramConfig(z["buckets"], 40503, 2971), canon_taps=z["taps"],
                          side_dim=z["side_dim"])
 
 
@@ -832,7 +832,7 @@ def sebavik_kernel_table(z, pk, page=16):
         emb = torch.randn(vocab, width, device=dev).to(bf)
         pair = torch.randn(z["buckets"] + 1, width, device=dev).to(bf)
         last = torch.zeros(nseq + 1, 1, dtype=torch.int32, device=dev)
-        ms = timed_device(lambda: (ops.embed_pair(emb, pair, b, last, stream, 2.0, z["buckets"], 31, 17),
+        ms = timed_device(lambda: (ops.embed_pair(emb, pair, b, last, stream, 2.0, z["buckets"], 40503, 2971),
                                    ops.last_token_update(b, last, b.query_tiles(SEQUENCE_TILE))), flush=flush)
         tms = timed_device(lambda: ops.embed_rows(emb, b.tokens, stream, scale=2.0), flush=flush)
         put(f"embedding_{label}", ms, frac_bytes(n * width * 8, ms), tms, frac_bytes(n * width * 6, tms), "copy bandwidth", "embedding")

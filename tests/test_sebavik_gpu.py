@@ -114,7 +114,7 @@ CUTS = [(1, 0), (1, 0), (2, 3), (1, 1), (6, 2), (2, 1), (1, 9), (7, 1), (3, 2)] 
 
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("width,vocab,buckets,mul_prev,mul_cur,scale", [(50, 30, 7, 3, 5, 0.5), (256, 300, 1021, 31, 17, 1.0),
+@pytest.mark.parametrize("width,vocab,buckets,mul_prev,mul_cur,scale", [(50, 30, 7, 3, 5, 0.5), (264, 300, 509, 37, 11, 1.0),
                                                                        (64, 1000, 1, 1000003, 999983, 8.0),
                                                                        (1500, 5000, 9973, 2000003, 3, 0.25)])
 def test_embedding_with_second_table_and_previous_token_across_steps(dtype, width, vocab, buckets, mul_prev, mul_cur, scale):
@@ -251,7 +251,7 @@ def test_scaled_sums_token_input_and_depth_average(dtype, width, entries):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 16, 24), (3, 1, 10, 12), (8, 1, 64, 48), (2, 2, 36, 4), (5, 5, 8, 40)])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 16, 24), (3, 1, 10, 12), (8, 1, 64, 80), (2, 2, 36, 4), (5, 5, 8, 40)])
 def test_biased_projections_and_mixed_values_into_the_pages(dtype, heads, kv_heads, dim, vdim):
     """The first mixing layer stores its values and keeps them in 32-bit; a later layer stores (1 - lambda) v + lambda
     v_first.  Two sequences in one step, pages in no order."""
@@ -291,7 +291,7 @@ def test_biased_projections_and_mixed_values_into_the_pages(dtype, heads, kv_hea
 
 
 # (the serving precision runs shapes with sizes in steps of 16 on the tensor cores, the others on the CUDA cores)
-ATTENTION_SHAPES = [(4, 2, 16, 24), (8, 1, 64, 48), (3, 3, 40, 8), (40, 1, 8, 16), (2, 1, 96, 200), (6, 2, 64, 32), (2, 2, 32, 256)]
+ATTENTION_SHAPES = [(4, 2, 16, 24), (8, 1, 64, 80), (3, 3, 40, 8), (40, 1, 8, 16), (2, 1, 96, 200), (6, 2, 64, 32), (2, 2, 32, 256)]
 
 
 def rounded(dtype, g, *shape):
@@ -363,7 +363,7 @@ def window_case(dtype, g, T, heads, kv_heads, dim, vdim, window, keep, cap):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 96, 24), (3, 1, 10, 12), (8, 1, 64, 48), (2, 2, 32, 32), (40, 1, 8, 16)])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 96, 24), (3, 1, 10, 12), (8, 1, 64, 80), (2, 2, 32, 32), (40, 1, 8, 16)])
 @pytest.mark.parametrize("window,keep", [(7, 0), (33, 2), (80, 4), (96, 20), (9, 18), (1, 1), (64, 16), (130, 40), (16, 17)])
 def test_window_edges_and_kept_first_keys(dtype, heads, kv_heads, dim, vdim, window, keep):
     """The key just outside a query's window is made to agree with it strongly (it would take all the weight if it

@@ -69,3 +69,5 @@ def _ensure_builtin() -> None:
         from ..models import favudra  # noqa: F401
     if "Sebavik" not in _ARCHITECTURES:
         from ..models import sebavik  # noqa: F401
+    if "Kezuvik" not in _ARCHITECTURES:
+        from ..models import kezuvik  # noqa: F401

@@ -1,0 +1,85 @@
+// Small element-wise steps of gated designs, float32 arithmetic in both precisions:
+//   sigmoid_gate   the output gate of a mixer: the heads' outputs times sigmoid(g), with one gate
+//                  number per entry or one per group of neighbouring entries (a head)
+//   glu_gelu       the gated feed-forward's inner step with the tanh form of GELU:
+//                  h = gelu_tanh(gate) * up for rows laid out [gate | up]
+//   softcap_rows   z <- cap * tanh(z / cap) on float32 rows (the logits' cap)
+#include "bw_act.cuh"
+
+#include <math.h>
+
+namespace {
+
+constexpr float kGeluCubic = 0.044715f;
+constexpr float kSqrt2OverPi = 0.7978845608028654f;
+
+__device__ __forceinline__ float sigmoid_f(float z) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-z))); }
+
+// gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  const float inner = __fmul_rn(kSqrt2OverPi, __fmaf_rn(__fmul_rn(kGeluCubic, __fmul_rn(z, z)), z, z));
+  return __fmul_rn(__fmul_rn(0.5f, z), __fadd_rn(1.0f, tanhf(inner)));
+}
+
+// v[r][c] *= sigmoid(g[r][c / group]); g is float32 with a row stride of its own.
+__global__ void sigmoid_gate_kernel(act_t* v, int cols, const float* __restrict__ g, int g_stride, int group, size_t count) {
+  bw::pdl_enter();
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const size_t r = i / cols;
+  const int c = static_cast<int>(i - r * cols);
+  v[i] = bw::from_f<act_t>(__fmul_rn(bw::to_f(v[i]), sigmoid_f(g[r * g_stride + c / group])));
+}
+
+__global__ void glu_gelu_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inter, size_t count) {
+  bw::pdl_enter();
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const size_t r = i / inter;
+  const int c = static_cast<int>(i - r * inter);
+  const act_t* g = gate_up + r * 2 * inter + c;
+  out[i] = bw::from_f<act_t>(__fmul_rn(gelu_tanh_f(bw::to_f(g[0])), bw::to_f(g[inter])));
+}
+
+__global__ void softcap_rows_kernel(float* z, float cap, size_t count) {
+  bw::pdl_enter();
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < count) z[i] = __fmul_rn(cap, tanhf(__fdiv_rn(z[i], cap)));
+}
+
+unsigned blocks_for(size_t count) { return static_cast<unsigned>((count + 255) / 256); }
+
+}  // namespace
+
+// v: [n, cols] in the activation type, gated in place; g: float32 rows of `g_stride` floats holding
+// cols / group gate numbers each.
+BW_API int BW_FN(sigmoid_gate)(void* v, int n, int cols, const float* g, int g_stride, int group, cudaStream_t stream) {
+  if (n <= 0 || cols <= 0) return 0;
+  if (group <= 0 || cols % group) {
+    bw::set_error("sigmoid_gate: %d columns are not whole groups of %d", cols, group);
+    return -1;
+  }
+  const size_t count = static_cast<size_t>(n) * cols;
+  bw::launch_pdl(sigmoid_gate_kernel, dim3(blocks_for(count)), dim3(256), 0, stream, static_cast<act_t*>(v), cols, g,
+                 g_stride, group, count);
+  return bw::launch_status();
+}
+
+BW_API int BW_FN(glu_gelu)(const void* gate_up, void* out, int n, int inter, cudaStream_t stream) {
+  if (n <= 0 || inter <= 0) return 0;
+  const size_t count = static_cast<size_t>(n) * inter;
+  bw::launch_pdl(glu_gelu_kernel, dim3(blocks_for(count)), dim3(256), 0, stream, static_cast<const act_t*>(gate_up),
+                 static_cast<act_t*>(out), inter, count);
+  return bw::launch_status();
+}
+
+BW_API int BW_FN(softcap_rows)(float* z, long long count, float cap, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (!(cap > 0.0f)) {
+    bw::set_error("softcap_rows: the cap must be positive, got %g", static_cast<double>(cap));
+    return -1;
+  }
+  bw::launch_pdl(softcap_rows_kernel, dim3(blocks_for(static_cast<size_t>(count))), dim3(256), 0, stream, z, cap,
+                 static_cast<size_t>(count));
+  return bw::launch_status();
+}

@@ -22,10 +22,25 @@ namespace {
 // ---------------------------------------------------------------------------------------
 // The rotation of pair i (entries 2i and 2i + 1 of a vector) by the table row of the
 // position: (u, v) -> (u cos - v sin, v cos + u sin). `pairs` pairs are turned, entries
-// from 2 * pairs on pass unchanged.
+// from 2 * pairs on pass unchanged. In the half layout (`half_layout` != 0) pair i is made of
+// entries i and i + pairs instead.
 __device__ __forceinline__ void turn(float u, float v, float c, float s, float& ru, float& rv) {
   ru = __fsub_rn(__fmul_rn(u, c), __fmul_rn(v, s));
   rv = __fadd_rn(__fmul_rn(v, c), __fmul_rn(u, s));
+}
+
+// Entry i of the vector `src` after the rotation in the half layout: entry i < pairs is the first of its
+// pair and entry i + pairs the second; entries from 2 * pairs on pass unchanged. `load` reads an entry
+// as float.
+template <typename Load>
+__device__ __forceinline__ float turned_half(Load load, int i, int pairs, const float* __restrict__ cos_row,
+                                             const float* __restrict__ sin_row) {
+  const float self = load(i);
+  if (i >= 2 * pairs) return self;
+  const int j = i < pairs ? i : i - pairs;
+  const float c = cos_row[j], s = sin_row[j];
+  return i < pairs ? __fsub_rn(__fmul_rn(self, c), __fmul_rn(load(i + pairs), s))
+                   : __fadd_rn(__fmul_rn(self, c), __fmul_rn(load(i - pairs), s));
 }
 
 // One block per row: d = the row of the down projection (float32, rank + rot_dim wide).
@@ -34,7 +49,7 @@ __global__ void __launch_bounds__(128)
 latent_store_kernel(const float* __restrict__ d, int d_stride, const float* __restrict__ w, float eps,
                     const int* __restrict__ pos, const int* __restrict__ row_seq, const float* __restrict__ cos_t,
                     const float* __restrict__ sin_t, int pairs, const int* __restrict__ block_table, int max_blocks,
-                    act_t* cache, int rank, int rot_dim, int page) {
+                    act_t* cache, int rank, int rot_dim, int page, int half_layout) {
   bw::pdl_enter();
   __shared__ float red[32];
   const int r = blockIdx.x;
@@ -47,6 +62,13 @@ latent_store_kernel(const float* __restrict__ d, int d_stride, const float* __re
   const float inv = bw::rms_scale(bw::block_sum(ss, red), rank, eps);
   for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = bw::from_f<act_t>(bw::rms_apply(dr[i], inv, w[i]));
   const float* kr = dr + rank;
+  if (half_layout) {
+    const float* cr = cos_t + static_cast<size_t>(p) * pairs;
+    const float* sr = sin_t + static_cast<size_t>(p) * pairs;
+    for (int i = threadIdx.x; i < rot_dim; i += blockDim.x)
+      dst[rank + i] = bw::from_f<act_t>(turned_half([&](int e) { return kr[e]; }, i, pairs, cr, sr));
+    return;
+  }
   for (int i = threadIdx.x; i < (rot_dim + 1) / 2; i += blockDim.x) {
     const float u = kr[2 * i];
     if (2 * i + 1 >= rot_dim) {  // an odd last entry has no partner
@@ -67,10 +89,21 @@ latent_store_kernel(const float* __restrict__ d, int d_stride, const float* __re
 __global__ void __launch_bounds__(128)
 rotate_heads_kernel(const act_t* __restrict__ q, int q_stride, int head_stride, int offset, act_t* out, int o_stride,
                     int out_head_stride, int out_offset, int heads, int rot_dim, int pairs, const int* __restrict__ pos,
-                    const float* __restrict__ cos_t, const float* __restrict__ sin_t) {
+                    const float* __restrict__ cos_t, const float* __restrict__ sin_t, int half_layout) {
   bw::pdl_enter();
   const int r = blockIdx.x;
   const int p = pos[r];
+  if (half_layout) {
+    const float* cr = cos_t + static_cast<size_t>(p) * pairs;
+    const float* sr = sin_t + static_cast<size_t>(p) * pairs;
+    for (int item = threadIdx.x; item < heads * rot_dim; item += blockDim.x) {
+      const int h = item / rot_dim, i = item - h * rot_dim;
+      const act_t* src = q + static_cast<size_t>(r) * q_stride + h * head_stride + offset;
+      out[static_cast<size_t>(r) * o_stride + h * out_head_stride + out_offset + i] =
+          bw::from_f<act_t>(turned_half([&](int e) { return bw::to_f(src[e]); }, i, pairs, cr, sr));
+    }
+    return;
+  }
   const int half = (rot_dim + 1) / 2;
   for (int item = threadIdx.x; item < heads * half; item += blockDim.x) {
     const int h = item / half, i = item - h * half;
@@ -100,6 +133,12 @@ rotate_heads_kernel(const act_t* __restrict__ q, int q_stride, int head_stride, 
 constexpr int kWarps = 8;
 constexpr int kKeys = 32;
 constexpr int kThreads = kWarps * 32;
+
+// A sink: a learned logit per head that joins the softmax's denominator once, with no key and no
+// value. `l` is the sum of exp(s - m) over the keys seen; `sinks` null: the sum stays as it is.
+__device__ __forceinline__ float with_sink(float l, float m, const float* __restrict__ sinks, int h) {
+  return sinks ? __fadd_rn(l, expf(__fsub_rn(sinks[h], m))) : l;
+}
 
 // One tile of keys in shared memory (`keys`, rows of `ks` floats) against the query `qv`
 // (`dk` floats in shared memory) of position `pq`: updates m, l and acc (entry i of acc is
@@ -159,7 +198,8 @@ latent_attention_kernel(const act_t* __restrict__ q, int q_stride, const act_t* 
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tile_seq,
                         const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                         const int* __restrict__ seq_pos0, const int* __restrict__ seq_row0, act_t* out, int o_stride,
-                        int heads, int hb, int rank, int rot_dim, int page, int window, float scale) {
+                        int heads, int hb, int rank, int rot_dim, int page, int window, float scale,
+                        const float* __restrict__ sinks) {
   bw::pdl_enter();
   extern __shared__ float sm[];
   const int dk = rank + rot_dim, ks = dk + 1;
@@ -204,7 +244,7 @@ latent_attention_kernel(const act_t* __restrict__ q, int q_stride, const act_t* 
     const int qi = warp + kWarps * j;
     if (qi >= nq) continue;
     act_t* dst = out + static_cast<size_t>(row0 + qi / nh) * o_stride + (h0 + qi % nh) * rank;
-    const float inv = __fdiv_rn(1.0f, l[j]);
+    const float inv = __fdiv_rn(1.0f, with_sink(l[j], m[j], sinks, h0 + qi % nh));
 #pragma unroll
     for (int i = 0; i < ACC; ++i) {
       const int d = i * 32 + lane;
@@ -265,7 +305,7 @@ latent_attention_split_kernel(const act_t* __restrict__ q, int q_stride, const a
 // One block per (row, head): folds the spans' records in ascending order.
 __global__ void __launch_bounds__(128)
 latent_attention_merge_kernel(const float* __restrict__ part, const int* __restrict__ pos, int spans, int span,
-                              int heads, int rank, act_t* out, int o_stride) {
+                              int heads, int rank, act_t* out, int o_stride, const float* __restrict__ sinks) {
   bw::pdl_enter();
   const int r = blockIdx.x, h = blockIdx.y;
   const float* rec0 = part + (static_cast<size_t>(r) * heads + h) * spans * (rank + 2);
@@ -277,7 +317,7 @@ latent_attention_merge_kernel(const float* __restrict__ part, const int* __restr
     const float* rec = rec0 + static_cast<size_t>(s) * (rank + 2);
     if (rec[0] != -INFINITY) l = __fmaf_rn(rec[1], expf(__fsub_rn(rec[0], m)), l);
   }
-  const float inv = __fdiv_rn(1.0f, l);
+  const float inv = __fdiv_rn(1.0f, with_sink(l, m, sinks, h));
   for (int d = threadIdx.x; d < rank; d += blockDim.x) {
     float a = 0.0f;
     for (int s = 0; s < used; ++s) {
@@ -312,7 +352,7 @@ latent_attention_tc_kernel(const act_t* __restrict__ q, int q_stride, const act_
                            const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                            const int* __restrict__ seq_pos0, const int* __restrict__ seq_row0, act_t* out, int o_stride,
                            float* __restrict__ part, int spans, int span, int heads, int hb, int rank, int rot_dim,
-                           int page, int window, float scale) {
+                           int page, int window, float scale, const float* __restrict__ sinks) {
   bw::pdl_enter();
   extern __shared__ __align__(16) unsigned char raw[];
   const int dk = rank + rot_dim, rs = dk + 8;  // row stride in elements: an odd number of 16-byte pieces
@@ -525,7 +565,7 @@ latent_attention_tc_kernel(const act_t* __restrict__ q, int q_stride, const act_
         if (d < rank) rec[2 + d] = acc[i][2 * half], rec[3 + d] = acc[i][2 * half + 1];
       }
     } else {
-      const float inv = __fdiv_rn(1.0f, l);
+      const float inv = __fdiv_rn(1.0f, with_sink(l, m, sinks, h));
       act_t* dst = out + static_cast<size_t>(row) * o_stride + h * rank;
 #pragma unroll
       for (int i = 0; i < NT; ++i) {
@@ -562,27 +602,30 @@ constexpr int kQueriesPerWarp = 4;
 BW_API int BW_FN(latent_store)(const float* d, int d_stride, const float* w, float eps, const int* pos,
                                const int* row_seq, const float* cos_t, const float* sin_t, int pairs,
                                const int* block_table, int max_blocks, act_t* cache, int n, int rank, int rot_dim,
-                               int page, cudaStream_t stream) {
+                               int page, int half_layout, cudaStream_t stream) {
   if (n <= 0) return 0;
+  if (half_layout && pairs == 0) half_layout = 0;
   if (rank <= 0 || rot_dim < 0 || 2 * pairs > rot_dim || (pairs > 0 && !cos_t)) {
     bw::set_error("latent_store: rank %d, rotated part %d, %d pairs", rank, rot_dim, pairs);
     return -1;
   }
   bw::launch_pdl(latent_store_kernel, dim3(n), dim3(128), 0, stream, d, d_stride, w, eps, pos, row_seq, cos_t, sin_t,
-                 pairs, block_table, max_blocks, cache, rank, rot_dim, page);
+                 pairs, block_table, max_blocks, cache, rank, rot_dim, page, half_layout);
   return bw::launch_status();
 }
 
 BW_API int BW_FN(rotate_heads)(const act_t* q, int q_stride, int head_stride, int offset, act_t* out, int o_stride,
                                int out_head_stride, int out_offset, int n, int heads, int rot_dim, int pairs,
-                               const int* pos, const float* cos_t, const float* sin_t, cudaStream_t stream) {
+                               const int* pos, const float* cos_t, const float* sin_t, int half_layout,
+                               cudaStream_t stream) {
   if (n <= 0 || heads <= 0 || rot_dim <= 0) return 0;
+  if (half_layout && pairs == 0) half_layout = 0;
   if (2 * pairs > rot_dim || (pairs > 0 && !cos_t)) {
     bw::set_error("rotate_heads: %d heads, rotated part %d, %d pairs", heads, rot_dim, pairs);
     return -1;
   }
   bw::launch_pdl(rotate_heads_kernel, dim3(n), dim3(128), 0, stream, q, q_stride, head_stride, offset, out, o_stride,
-                 out_head_stride, out_offset, heads, rot_dim, pairs, pos, cos_t, sin_t);
+                 out_head_stride, out_offset, heads, rot_dim, pairs, pos, cos_t, sin_t, half_layout);
   return bw::launch_status();
 }
 
@@ -597,7 +640,7 @@ BW_API int BW_FN(latent_attention)(const act_t* q, int q_stride, const act_t* ca
                                    int max_blocks, const int* tile_seq, const int* tile_row0, const int* tile_rows,
                                    int tiles, const int* seq_pos0, const int* seq_row0, act_t* out, int o_stride,
                                    int heads, int rank, int rot_dim, int page, int window, float scale,
-                                   cudaStream_t stream) {
+                                   const float* sinks, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   const int q_max = kWarps * kQueriesPerWarp;
   const int hb = heads < q_max ? heads : q_max;
@@ -614,7 +657,7 @@ BW_API int BW_FN(latent_attention)(const act_t* q, int q_stride, const act_t* ca
     if (int rc = raise_smem(kernel, smem)) return rc;                                                               \
     bw::launch_pdl(kernel, grid, dim3(kThreads), smem, stream, q, q_stride, cache, block_table, max_blocks, tile_seq, \
                    tile_row0, tile_rows, seq_pos0, seq_row0, out, o_stride, heads, hb, rank, rot_dim, page, window, \
-                   scale);                                                                                          \
+                   scale, sinks);                                                                                   \
   }
   if (rank <= 128) BW_LAUNCH(4) else if (rank <= 256) BW_LAUNCH(8) else BW_LAUNCH(16)
 #undef BW_LAUNCH
@@ -637,7 +680,7 @@ BW_API int BW_FN(latent_attention_spans)(int n, int heads, int max_keys, int* sp
 BW_API int BW_FN(latent_attention_split)(const act_t* q, int q_stride, const act_t* cache, const int* block_table,
                                          int max_blocks, const int* row_seq, const int* pos, act_t* out, int o_stride,
                                          int n, int heads, int rank, int rot_dim, int page, int window, float scale,
-                                         int max_keys, float* scratch, cudaStream_t stream) {
+                                         int max_keys, float* scratch, const float* sinks, cudaStream_t stream) {
   if (n <= 0) return 0;
   int span = 0;
   const int spans = BW_FN(latent_attention_spans)(n, heads, max_keys, &span);
@@ -658,7 +701,7 @@ BW_API int BW_FN(latent_attention_split)(const act_t* q, int q_stride, const act
 #undef BW_LAUNCH
   if (int rc = bw::launch_status()) return rc;
   bw::launch_pdl(latent_attention_merge_kernel, dim3(n, heads), dim3(128), 0, stream, scratch, pos, spans, span, heads,
-                 rank, out, o_stride);
+                 rank, out, o_stride, sinks);
   return bw::launch_status();
 }
 
@@ -699,7 +742,7 @@ BW_API int BW_FN(latent_attention_tc)(const act_t* q, int q_stride, const act_t*
                                       int max_blocks, const int* tile_seq, const int* tile_row0, const int* tile_rows,
                                       int tiles, const int* seq_pos0, const int* seq_row0, const int* pos, act_t* out,
                                       int o_stride, int n, int heads, int rank, int rot_dim, int page, int window,
-                                      float scale, int max_keys, float* scratch, cudaStream_t stream) {
+                                      float scale, int max_keys, float* scratch, const float* sinks, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (!BW_FN(latent_attention_tc_tile_rows)(heads, rank, rot_dim, q_stride) || o_stride % 2) {
     bw::set_error("latent attention: the tensor-core kernel does not take rank %d with rotated part %d", rank, rot_dim);
@@ -717,14 +760,14 @@ BW_API int BW_FN(latent_attention_tc)(const act_t* q, int q_stride, const act_t*
     if (int rc = raise_smem(kernel, smem)) return rc;                                                              \
     bw::launch_pdl(kernel, grid, dim3(128 * CS), smem, stream, q, q_stride, cache, block_table, max_blocks,        \
                    tile_seq, tile_row0, tile_rows, seq_pos0, seq_row0, out, o_stride, scratch, spans, span, heads, \
-                   hb, rank, rot_dim, page, window, scale);                                                        \
+                   hb, rank, rot_dim, page, window, scale, sinks);                                                 \
   }
   if (rank <= 128) BW_LAUNCH(16, 1) else if (rank <= 256) BW_LAUNCH(32, 1) else BW_LAUNCH(32, 2)
 #undef BW_LAUNCH
   if (int rc = bw::launch_status()) return rc;
   if (scratch) {
     bw::launch_pdl(latent_attention_merge_kernel, dim3(n, heads), dim3(128), 0, stream, scratch, pos, spans, span, heads,
-                   rank, out, o_stride);
+                   rank, out, o_stride, sinks);
     return bw::launch_status();
   }
   return 0;

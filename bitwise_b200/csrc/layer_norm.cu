@@ -45,6 +45,51 @@ layernorm_kernel(const float* x, const float* __restrict__ w1, const float* __re
   }
 }
 
+// The layer norm that follows a sublayer in blocks with a norm on both sides of each sublayer:
+// x += (d - mean(d)) / sqrt(var(d) + eps) * w, with d the sublayer's output (float32) and x the
+// float32 stream; a constant factor on what is added is folded into w by the caller. Where the
+// next sublayer's layer norm follows at once, the same block forms it from the row it has just
+// summed: xn = (x - mean(x)) / sqrt(var(x) + eps') * w', one kernel instead of two.
+__global__ void __launch_bounds__(kThreads)
+layernorm_residual_kernel(const float* __restrict__ d, const float* __restrict__ w, float* x, int width, float eps,
+                          const float* __restrict__ w_next, float eps_next, act_t* xn) {
+  bw::pdl_enter();
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const size_t base = static_cast<size_t>(blockIdx.x) * width;
+  const float fw = static_cast<float>(width);
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < width; i += kThreads) {
+    const float v = d[base + i];
+    row[i] = v;
+    s = __fadd_rn(s, v);
+  }
+  const float mean = __fdiv_rn(bw::block_sum(s, red), fw);
+  float q = 0.0f;
+  for (int i = threadIdx.x; i < width; i += kThreads) {
+    const float c = __fsub_rn(row[i], mean);
+    q = __fmaf_rn(c, c, q);
+  }
+  const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(bw::block_sum(q, red), fw), eps)));
+  float s2 = 0.0f;
+  for (int i = threadIdx.x; i < width; i += kThreads) {
+    const float v = __fadd_rn(x[base + i], __fmul_rn(__fmul_rn(__fsub_rn(row[i], mean), inv), w[i]));
+    x[base + i] = v;
+    row[i] = v;  // (each thread reads back only what it wrote)
+    s2 = __fadd_rn(s2, v);
+  }
+  if (!xn) return;
+  const float mean2 = __fdiv_rn(bw::block_sum(s2, red), fw);
+  float q2 = 0.0f;
+  for (int i = threadIdx.x; i < width; i += kThreads) {
+    const float c = __fsub_rn(row[i], mean2);
+    q2 = __fmaf_rn(c, c, q2);
+  }
+  const float inv2 = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(bw::block_sum(q2, red), fw), eps_next)));
+  for (int i = threadIdx.x; i < width; i += kThreads)
+    xn[base + i] = bw::from_f<act_t>(__fmul_rn(__fmul_rn(__fsub_rn(row[i], mean2), inv2), w_next[i]));
+}
+
 // x += d, element by element (the residual sum of a block whose parts wrote into d).
 __global__ void add_rows_kernel(float* x, const float* __restrict__ d, size_t count) {
   bw::pdl_enter();
@@ -69,6 +114,19 @@ BW_API int BW_FN(layernorm)(const float* x, const float* w1, const float* w2, vo
   else
     bw::launch_pdl(layernorm_kernel<act_t>, dim3(n), dim3(kThreads), smem, stream, x, w1, w2, static_cast<act_t*>(y1),
                    static_cast<act_t*>(y2), rows, width, eps);
+  return bw::launch_status();
+}
+
+// w_next, xn: the layer norm of the summed row into xn (activation type) as well; both null for none.
+BW_API int BW_FN(layernorm_residual)(const float* d, const float* w, float* x, int n, int width, float eps,
+                                     const float* w_next, float eps_next, void* xn, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (width <= 0 || width > 48 * 1024 / 4) {
+    bw::set_error("layernorm_residual: width %d (1 .. 12288)", width);
+    return -1;
+  }
+  bw::launch_pdl(layernorm_residual_kernel, dim3(n), dim3(kThreads), static_cast<size_t>(width) * sizeof(float), stream,
+                 d, w, x, width, eps, w_next, eps_next, static_cast<act_t*>(w_next ? xn : nullptr));
   return bw::launch_status();
 }
 

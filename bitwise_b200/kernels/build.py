@@ -47,6 +47,9 @@ KERNEL_SETS: Dict[str, List[tuple]] = {
     # a per-layer token input and an average over the layers' results; the embedding with a second table
     "f32_stream": [("common.cu", []), ("stream_ops.cu", ["-DBW_ACT_BF16=0"])],
     "bf16_stream": [("common.cu", []), ("stream_ops.cu", ["-DBW_ACT_BF16=1"])],
+    # element-wise steps of gated designs: a mixer's output gate, the GELU form of the gated feed-forward, capped logits
+    "f32_gated": [("common.cu", []), ("gated_ops.cu", ["-DBW_ACT_BF16=0"])],
+    "bf16_gated": [("common.cu", []), ("gated_ops.cu", ["-DBW_ACT_BF16=1"])],
 }
 
 # head sizes whose attention library a full build prepares (others are compiled when a model asks)
@@ -225,6 +228,6 @@ def build_all(verbose: bool = True) -> List[str]:
     """Compile every kernel set (what a 'does it build' check wants)."""
     out = [ensure_host_built(verbose)]
     out += [ensure_built(k, (), verbose) for k in ("f32", "bf16", "f32_parts", "bf16_parts", "f32_mixers", "bf16_mixers",
-                                                         "f32_stream", "bf16_stream")]
+                                                         "f32_stream", "bf16_stream", "f32_gated", "bf16_gated")]
     out += [ensure_built("bf16_attn", (f"BW_HEAD_DIM={hd}",), verbose) for hd in DEFAULT_HEAD_DIMS]
     return out

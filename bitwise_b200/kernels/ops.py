@@ -45,9 +45,21 @@ def _need(t: torch.Tensor, dtype, what: str, dims: Optional[int] = None) -> None
         raise KernelError(f"{what}: expected {dims} dimensions, got {tuple(t.shape)}")
 
 
+def _need_rows(t: torch.Tensor, dtype, what: str) -> None:
+    """A matrix whose rows are contiguous; the rows may lie apart (columns sliced out of wider rows)."""
+    if not t.is_cuda:
+        raise KernelError(f"{what}: tensor is on {t.device}; the kernels run on a CUDA device only")
+    if t.dtype != dtype:
+        raise KernelError(f"{what}: expected {dtype}, got {t.dtype}")
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1) or t.stride(0) < t.shape[1]:
+        raise KernelError(f"{what}: expected rows of contiguous entries, got shape {tuple(t.shape)} strides {t.stride()}")
+
+
 class KernelOps:
     """Operations of one precision.  ``act_dtype`` is the dtype of activations between
     kernels (the residual stream, logits and norm weights are float32 in both)."""
+
+    FUSED_ACTIVATIONS = ("silu",)  # what the gate/up product can apply in its epilogue
 
     def __init__(self, dtype: str, verbose_build: bool = True):
         if dtype not in ("float32", "bfloat16"):
@@ -203,10 +215,10 @@ class KernelOps:
                        _c_int(int(legacy)), self._stream(),
                        launches=1 if legacy else self._linear_kernels(m, n, k, False, partials is not None))
 
-    def fuses_swiglu(self, width: int, intermediate: int) -> bool:
-        """Whether ``linear_swiglu`` can take a feed-forward of these sizes (then its gate/up
-        weights are to be interleaved with ``interleave_gate_up``)."""
-        return self.kind == "bf16" and intermediate % 64 == 0 and width % 8 == 0
+    def fuses_swiglu(self, width: int, intermediate: int, activation: str = "silu") -> bool:
+        """Whether ``linear_swiglu`` can take a feed-forward of these sizes and this activation (then its
+        gate/up weights are to be interleaved with ``interleave_gate_up``)."""
+        return self.kind == "bf16" and intermediate % 64 == 0 and width % 8 == 0 and activation in self.FUSED_ACTIVATIONS
 
     @staticmethod
     def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -629,6 +641,28 @@ class KernelOps:
                     _c_int(int(out.dtype == torch.float32)), _p(rows), _c_int(n), _c_int(width), _c_float(eps),
                     self._stream())
 
+    def layernorm_residual(self, d: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tensor,
+                           next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
+                           next_out: Optional[torch.Tensor] = None) -> None:
+        """x[r] += (d[r] - mean) / sqrt(var + eps) * weight with the row statistics of d; d, weight and x
+        float32.  With ``next_weight`` and ``next_out`` (act_dtype) also the layer norm of the summed row, with
+        that weight and ``next_eps``: the norm before the next sublayer, in the same kernel."""
+        n, width = x.shape
+        _need(d, torch.float32, "layernorm_residual d", 2)
+        _need(x, torch.float32, "layernorm_residual x", 2)
+        _need(weight, torch.float32, "layernorm_residual weight", 1)
+        if tuple(d.shape) != (n, width) or weight.shape[0] != width:
+            raise KernelError("layernorm_residual: shapes differ")
+        if (next_weight is None) != (next_out is None):
+            raise KernelError("layernorm_residual: the next norm needs a weight and an output")
+        if next_out is not None:
+            _need(next_weight, torch.float32, "layernorm_residual next_weight", 1)
+            _need(next_out, self.act_dtype, "layernorm_residual next_out", 2)
+            if tuple(next_out.shape) != (n, width) or next_weight.shape[0] != width:
+                raise KernelError("layernorm_residual: the next norm's shapes differ")
+        self._pcall("layernorm_residual", _p(d), _p(weight), _p(x), _c_int(n), _c_int(width), _c_float(eps),
+                    _p(next_weight), _c_float(next_eps), _p(next_out), self._stream())
+
     def add_rows(self, x: torch.Tensor, d: torch.Tensor) -> None:
         """x += d (float32, same shape)."""
         _need(x, torch.float32, "add_rows x")
@@ -639,24 +673,24 @@ class KernelOps:
 
     def latent_store(self, d: torch.Tensor, weight: torch.Tensor, eps: float, pos: torch.Tensor, row_seq: torch.Tensor,
                      cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], block_table: torch.Tensor,
-                     cache: torch.Tensor, rank: int, rot_dim: int) -> None:
-        """For every row of ``d`` (float32 [n, rank + rot_dim]): the first ``rank`` entries divided by
-        their root mean square (eps inside the root) times ``weight``, the last ``rot_dim`` turned pair
-        by pair (2i with 2i+1) by row ``pos`` of the tables, both stored at the row's place in ``cache``
-        [pages, page, rank + rot_dim]."""
+                     cache: torch.Tensor, rank: int, rot_dim: int, half_layout: bool = False) -> None:
+        """For every row of ``d`` (float32 [n, >= rank + rot_dim], the row's first columns are used): the
+        first ``rank`` entries divided by their root mean square (eps inside the root) times ``weight``, the
+        next ``rot_dim`` turned pair by pair (2i with 2i+1; ``half_layout``: i with i + pairs) by row ``pos``
+        of the tables, both stored at the row's place in ``cache`` [pages, page, rank + rot_dim]."""
         n = d.shape[0]
-        _need(d, torch.float32, "latent_store d", 2)
+        _need_rows(d, torch.float32, "latent_store d")
         _need(weight, torch.float32, "latent_store weight", 1)
         _need(pos, torch.int32, "latent_store pos")
         _need(row_seq, torch.int32, "latent_store row_seq")
         _need(block_table, torch.int32, "latent_store block_table", 2)
         _need(cache, self.act_dtype, "latent_store cache", 3)
-        if d.shape[1] != rank + rot_dim or cache.shape[2] != rank + rot_dim or weight.shape[0] != rank:
+        if d.shape[1] < rank + rot_dim or cache.shape[2] != rank + rot_dim or weight.shape[0] != rank:
             raise KernelError("latent_store: widths do not fit rank + rot_dim")
         pairs = self._check_tables(cos, sin, rot_dim, "latent_store")
-        self._pcall("latent_store", _p(d), _c_int(d.shape[1]), _p(weight), _c_float(eps), _p(pos), _p(row_seq), _p(cos),
+        self._pcall("latent_store", _p(d), _c_int(d.stride(0)), _p(weight), _c_float(eps), _p(pos), _p(row_seq), _p(cos),
                     _p(sin), _c_int(pairs), _p(block_table), _c_int(block_table.shape[1]), _p(cache), _c_int(n),
-                    _c_int(rank), _c_int(rot_dim), _c_int(cache.shape[1]), self._stream())
+                    _c_int(rank), _c_int(rot_dim), _c_int(cache.shape[1]), _c_int(int(bool(half_layout))), self._stream())
 
     @staticmethod
     def _check_tables(cos, sin, rot_dim: int, what: str) -> int:
@@ -670,9 +704,10 @@ class KernelOps:
 
     def rotate_heads(self, q: torch.Tensor, heads: int, head_stride: int, offset: int, rot_dim: int, out: torch.Tensor,
                      out_head_stride: int, out_offset: int, pos: torch.Tensor, cos: Optional[torch.Tensor],
-                     sin: Optional[torch.Tensor]) -> None:
+                     sin: Optional[torch.Tensor], half_layout: bool = False) -> None:
         """out[r, h * out_head_stride + out_offset + i] = the entries q[r, h * head_stride + offset + i],
-        i < rot_dim, turned pair by pair (2i with 2i+1) by row pos[r] of the tables."""
+        i < rot_dim, turned pair by pair (2i with 2i+1; ``half_layout``: i with i + pairs) by row pos[r] of
+        the tables."""
         n = q.shape[0]
         _need(q, self.act_dtype, "rotate_heads q", 2)
         _need(out, self.act_dtype, "rotate_heads out", 2)
@@ -683,7 +718,7 @@ class KernelOps:
         pairs = self._check_tables(cos, sin, rot_dim, "rotate_heads")
         self._pcall("rotate_heads", _p(q), _c_int(q.shape[1]), _c_int(head_stride), _c_int(offset), _p(out),
                     _c_int(out.shape[1]), _c_int(out_head_stride), _c_int(out_offset), _c_int(n), _c_int(heads),
-                    _c_int(rot_dim), _c_int(pairs), _p(pos), _p(cos), _p(sin), self._stream())
+                    _c_int(rot_dim), _c_int(pairs), _p(pos), _p(cos), _p(sin), _c_int(int(bool(half_layout))), self._stream())
 
     def latent_attention_tile_rows(self, heads: int) -> int:
         """Rows of one sequence per query tile that ``latent_attention`` wants prepared."""
@@ -721,9 +756,11 @@ class KernelOps:
         return self._attn_scratch
 
     def latent_attention(self, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, out: torch.Tensor,
-                         heads: int, rank: int, rot_dim: int, scale: float, batch, window: int = 0) -> None:
+                         heads: int, rank: int, rot_dim: int, scale: float, batch, window: int = 0,
+                         sinks: Optional[torch.Tensor] = None) -> None:
         """out[r, h] = sum_j softmax_j(q[r, h] . cache[j] * scale) cache[j][:rank] over the cached
-        positions j <= pos[r] of row r's sequence (from pos - window + 1 on when window > 0).
+        positions j <= pos[r] of row r's sequence (from pos - window + 1 on when window > 0).  ``sinks``
+        (float32 [heads]): exp(sinks[h]) joins the softmax's denominator, with no key and no value.
         q: [n, heads * (rank + rot_dim)] (the heads' key maps folded in, the rotated part turned),
         cache: [pages, page, rank + rot_dim], out: [n, heads * rank]."""
         n = q.shape[0]
@@ -734,6 +771,10 @@ class KernelOps:
         _need(block_table, torch.int32, "latent_attention block_table", 2)
         if q.shape[1] != heads * dk or cache.shape[2] != dk or tuple(out.shape) != (n, heads * rank):
             raise KernelError("latent_attention: shapes do not fit heads * (rank + rot_dim)")
+        if sinks is not None:
+            _need(sinks, torch.float32, "latent_attention sinks", 1)
+            if sinks.shape[0] != heads:
+                raise KernelError("latent_attention: one sink per head is needed")
         page = cache.shape[1]
         tc_rows = self._latent_tc_rows(heads, rank, rot_dim)
         if tc_rows and (not hasattr(batch, "tile_sets") or tc_rows in batch.tile_sets):
@@ -750,7 +791,7 @@ class KernelOps:
                         _c_int(block_table.shape[1]), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count),
                         _p(batch.seq_pos0), _p(batch.seq_row0), _p(batch.pos), _p(out), _c_int(out.shape[1]), _c_int(n),
                         _c_int(heads), _c_int(rank), _c_int(rot_dim), _c_int(page), _c_int(window), _c_float(scale),
-                        _c_int(batch.max_keys), _p(scratch), self._stream(), launches=launches)
+                        _c_int(batch.max_keys), _p(scratch), _p(sinks), self._stream(), launches=launches)
             return
         t_seq, t_row0, t_rows, t_count = batch.query_tiles(self.latent_attention_tile_rows(heads))
         if t_count == n and batch.max_keys > 256:
@@ -763,12 +804,13 @@ class KernelOps:
             self._pcall("latent_attention_split", _p(q), _c_int(q.shape[1]), _p(cache), _p(block_table),
                         _c_int(block_table.shape[1]), _p(batch.row_seq), _p(batch.pos), _p(out), _c_int(out.shape[1]),
                         _c_int(n), _c_int(heads), _c_int(rank), _c_int(rot_dim), _c_int(page), _c_int(window),
-                        _c_float(scale), _c_int(batch.max_keys), _p(self._attn_scratch), self._stream(), launches=2)
+                        _c_float(scale), _c_int(batch.max_keys), _p(self._attn_scratch), _p(sinks), self._stream(),
+                        launches=2)
             return
         self._pcall("latent_attention", _p(q), _c_int(q.shape[1]), _p(cache), _p(block_table),
                     _c_int(block_table.shape[1]), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count), _p(batch.seq_pos0),
                     _p(batch.seq_row0), _p(out), _c_int(out.shape[1]), _c_int(heads), _c_int(rank), _c_int(rot_dim),
-                    _c_int(page), _c_int(window), _c_float(scale), self._stream())
+                    _c_int(page), _c_int(window), _c_float(scale), _p(sinks), self._stream())
 
     def route(self, logits: torch.Tensor, correction: Optional[torch.Tensor], groups: int, keep: int, top: int,
               weight_scale: float, chosen: torch.Tensor, weights: torch.Tensor, softmax_top: bool = False) -> None:
@@ -895,6 +937,59 @@ class KernelOps:
                 raise KernelError("combine: one factor per column is needed")
         self._pcall("combine", _p(x), _p(d), _p(y), _p(place), _p(weights), _c_int(n), _c_int(top), _c_int(width),
                     _p(scale), self._stream())
+
+    # -- element-wise steps of gated designs (their library is loaded at first use) ---------------------
+    def _gated_lib(self):
+        lib = getattr(self, "_gated", None)
+        if lib is None:
+            path = build.ensure_built(f"{self.kind}_gated", (), self._verbose_build)
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+            lib.bw_last_error.restype = ctypes.c_char_p
+            if self._failure_word is not None:
+                lib.bw_set_failure_word(_p(self._failure_word))
+            self._gated = lib
+            self._gated_fns = {}
+        return lib
+
+    def _gcall(self, name: str, *args) -> None:
+        lib = self._gated_lib()
+        fn = self._gated_fns.get(name)
+        if fn is None:
+            fn = getattr(lib, f"bw_{self.kind}_{name}")
+            fn.restype = _c_int
+            self._gated_fns[name] = fn
+        rc = fn(*args)
+        if rc != 0:
+            raise KernelError(f"{name} failed ({rc}): " + lib.bw_last_error().decode("utf-8", "replace"))
+        self.launches += 1
+
+    def sigmoid_gate(self, v: torch.Tensor, g: torch.Tensor, group: int = 1) -> None:
+        """v[r, c] *= sigmoid(g[r, c // group]) in place; v: act_dtype [n, cols], g: float32 [n, cols / group]
+        (its rows may be a slice of wider rows)."""
+        n, cols = v.shape
+        _need(v, self.act_dtype, "sigmoid_gate v", 2)
+        _need_rows(g, torch.float32, "sigmoid_gate g")
+        if group <= 0 or cols % group or tuple(g.shape) != (n, cols // group):
+            raise KernelError(f"sigmoid_gate: {tuple(g.shape)} gate numbers do not fit {cols} columns in groups of {group}")
+        self._gcall("sigmoid_gate", _p(v), _c_int(n), _c_int(cols), _p(g), _c_int(g.stride(0)), _c_int(group), self._stream())
+
+    def glu_gelu(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
+        """out = gelu_tanh(gate) * up for rows laid out [gate | up], gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2 / pi)
+        (z + 0.044715 z^3)))."""
+        n, inter = out.shape
+        _need(gate_up, self.act_dtype, "glu_gelu gate_up", 2)
+        _need(out, self.act_dtype, "glu_gelu out", 2)
+        if gate_up.shape[1] != 2 * inter or gate_up.shape[0] != n:
+            raise KernelError("glu_gelu: input is not [rows, 2 * inner]")
+        self._gcall("glu_gelu", _p(gate_up), _p(out), _c_int(n), _c_int(inter), self._stream())
+
+    def softcap_rows(self, z: torch.Tensor, cap: float) -> None:
+        """z <- cap * tanh(z / cap) in place on float32 rows."""
+        _need(z, torch.float32, "softcap_rows z")
+        self._gcall("softcap_rows", _p(z), ctypes.c_longlong(z.numel()), _c_float(cap), self._stream())
 
     # -- mixers with state beside or instead of pages, and the norm after a sublayer (their library
     #    is loaded at first use) -------------------------------------------------------------------

@@ -86,8 +86,13 @@ class OutputHead(Part):
     graph_safe = True  # kernels only: a step through this part can be captured
 
     def __init__(self, vocab: int, width: int, norm: Norm, tied_to: Optional[TokenEmbedding] = None,
-                 norm_name: str = "model.norm", head_name: str = "lm_head", suffix: str = ".weight"):
-        """A constant scale of the logits belongs to ``norm`` as its ``gain`` (the product is linear)."""
+                 norm_name: str = "model.norm", head_name: str = "lm_head", suffix: str = ".weight",
+                 softcap: Optional[float] = None):
+        """A constant scale of the logits belongs to ``norm`` as its ``gain`` (the product is linear).
+        ``softcap``: the logits become ``softcap * tanh(logits / softcap)``."""
+        if softcap is not None and not softcap > 0:
+            raise ValueError(f"the logits' cap must be positive, got {softcap!r}")
+        self.softcap = float(softcap) if softcap is not None else None
         self.vocab, self.width = vocab, width
         self.suffix = suffix
         self.norm, self.tied_to = norm, tied_to
@@ -116,4 +121,6 @@ class OutputHead(Part):
         self.norm.forward(ctx, x, last, rows=ctx.logit_rows)
         logits = ctx.workspace.rows("logits", c, self.vocab, torch.float32, growable=True)
         ctx.ops.linear(last, self.weight, logits)
+        if self.softcap is not None:
+            ctx.ops.softcap_rows(logits, self.softcap)
         return logits

@@ -14,9 +14,15 @@ latents per head, and the value map is applied to that sum.  The same arithmetic
 portions and single rows, so a position's result does not depend on how the prompt was cut.
 
 Rotation: entries 2i and 2i + 1 of the rotated part form pair i, turned by ``pos * base ** (-2i
-/ dims)``; ``rot_pairs`` pairs are turned and the rest of the part passes unchanged.  A layer
+/ dims)``; ``rot_pairs`` pairs are turned and the rest of the part passes unchanged.  A position
+encoding whose ``layout`` is "half" pairs entry i with entry i + dims / 2 instead.  A layer
 may read the cache of an earlier layer instead of writing one (``shares_cache``): it then has
 no down projection for keys and values.
+
+Options: ``sink`` (a learned logit per head, tensor ``sink``, whose exponential joins the softmax's
+denominator: it has no key and no value and is not scaled) and ``gate`` ("entry" or "head": the
+heads' values are multiplied by the sigmoid of a projection of the mixer's input, per entry or
+per head, before the output projection; :class:`OutputGate`).
 """
 from __future__ import annotations
 
@@ -26,17 +32,19 @@ import torch
 
 from ..weights.loader import KEEP32, MATRIX, ParamSpec
 from .base import Mixer, PagedLatentNeed, PagedLatentView, PositionEncoding, StepContext, register_mixer
+from .gate import OutputGate
 
 
 class LatentAttention(Mixer):
     graph_safe = True  # kernels only; launches depend on the step's sizes and ctx.max_keys
 
     NAMES = {"q": "q", "q_down": "dq", "q_norm": "dq.norm", "q_up": "uq", "kv_down": "dkv", "kv_norm": "dkv.norm",
-             "k_up": "uk", "v_up": "uv", "out": "o"}
+             "k_up": "uk", "v_up": "uv", "out": "o", "sink": "sink", "gate": "g"}
 
     def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, rank: int, scale: float, eps: float,
                  position: Optional[PositionEncoding] = None, q_rank: Optional[int] = None,
-                 shares_cache: bool = False, window: Optional[int] = None, names: Optional[Dict[str, str]] = None):
+                 shares_cache: bool = False, window: Optional[int] = None, names: Optional[Dict[str, str]] = None,
+                 sink: bool = False, gate: Optional[str] = None):
         for what, v in (("heads", heads), ("dim", dim), ("vdim", vdim), ("rank", rank)):
             if v <= 0:
                 raise ValueError(f"latent attention: {what} must be positive, got {v}")
@@ -49,6 +57,14 @@ class LatentAttention(Mixer):
         self.q_width = heads * (dim + rot_dim)
         self.w_q = self.w_q_down = self.q_norm = self.w_kv_down = self.kv_norm = None
         self.w_k_fold = self.w_v_up = self.w_o = None
+        self.sink, self.sinks = bool(sink), None
+        self.gate = OutputGate(width, heads, vdim, gate, self.names["gate"]) if gate else None
+        self.half_layout = getattr(position, "layout", "pairs") == "half"
+
+    @property
+    def _layout(self):
+        # (only the half layout is named to the kernels, so that earlier designs' calls stay as they were)
+        return {"half_layout": True} if self.half_layout else {}
 
     def cache_need(self):
         return PagedLatentNeed(self.rank, self.rot_dim, self.window)
@@ -73,6 +89,10 @@ class LatentAttention(Mixer):
         specs += [ParamSpec(f"{prefix}.{n['k_up']}", (self.heads * self.dim, self.rank), MATRIX),
                   ParamSpec(f"{prefix}.{n['v_up']}", (self.heads * self.vdim, self.rank), MATRIX),
                   ParamSpec(f"{prefix}.{n['out']}", (self.width, self.heads * self.vdim), MATRIX)]
+        if self.sink:
+            specs.append(ParamSpec(f"{prefix}.{n['sink']}", (self.heads,), KEEP32))
+        if self.gate is not None:
+            specs += self.gate.param_specs(prefix)
         return specs
 
     def load_params(self, state: Dict[str, torch.Tensor], prefix: str) -> None:
@@ -91,10 +111,16 @@ class LatentAttention(Mixer):
         self.w_k_fold = w_uk.reshape(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
         self.w_v_up = state[f"{prefix}.{n['v_up']}"].reshape(self.heads, self.vdim, self.rank).contiguous()
         self.w_o = state[f"{prefix}.{n['out']}"]
+        if self.sink:
+            self.sinks = state[f"{prefix}.{n['sink']}"]
+        if self.gate is not None:
+            self.gate.load_params(state, prefix)
 
     def param_bytes(self) -> int:
-        ts = (self.w_q, self.w_q_down, self.q_norm, self.w_kv_down, self.kv_norm, self.w_k_fold, self.w_v_up, self.w_o)
-        return sum(t.numel() * t.element_size() for t in ts if t is not None)
+        ts = (self.w_q, self.w_q_down, self.q_norm, self.w_kv_down, self.kv_norm, self.w_k_fold, self.w_v_up, self.w_o,
+              self.sinks)
+        return sum(t.numel() * t.element_size() for t in ts if t is not None) + (
+            self.gate.param_bytes() if self.gate is not None else 0)
 
     def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, cache: PagedLatentView,
                 accumulate: bool = True) -> None:
@@ -119,18 +145,20 @@ class LatentAttention(Mixer):
             d = ws.rows("latent_kv32", n, dk, torch.float32)
             ops.linear(xn, self.w_kv_down, d)
             ops.latent_store(d, self.kv_norm, self.eps, ctx.pos, ctx.row_seq, cos, sin, cache.block_table, cache.latent,
-                             self.rank, self.rot_dim)
+                             self.rank, self.rot_dim, **self._layout)
         # the key maps folded into the queries, the rotated parts beside them
         qf = ws.rows("latent_folded_q", n, self.heads * dk, act)
         ops.grouped_linear(q, self.w_k_fold, qf, n, x_group_cols=self.dim + self.rot_dim, o_group_cols=dk)
         if self.rot_dim:
             ops.rotate_heads(q, self.heads, self.dim + self.rot_dim, self.dim, self.rot_dim, qf, dk, self.rank, ctx.pos,
-                             cos, sin)
+                             cos, sin, **self._layout)
         mixed = ws.rows("latent_mixed", n, self.heads * self.rank, act)
         ops.latent_attention(qf, cache.latent, cache.block_table, mixed, self.heads, self.rank, self.rot_dim, self.scale,
-                             ctx, self.window or 0)
+                             ctx, self.window or 0, **({"sinks": self.sinks} if self.sink else {}))
         values = ws.rows("latent_values", n, self.heads * self.vdim, act)
         ops.grouped_linear(mixed, self.w_v_up, values, n, x_group_cols=self.rank, o_group_cols=self.vdim)
+        if self.gate is not None:
+            self.gate.apply(ctx, xn, values)
         ops.linear(values, self.w_o, x, residual=x if accumulate else None)
 
 

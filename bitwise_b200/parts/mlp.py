@@ -1,7 +1,9 @@
 """The dense SwiGLU feed-forward: ``h = silu(xn Wg^T) * (xn Wu^T)``, ``x += h Wd^T``
 (src/model.cpp:301-305; src/kernels.cpp:291-298).  gate_proj and up_proj are stacked by
 rows into one matrix so that one product yields rows laid out [gate | up]
-(src/model.cpp:162-164).  SiLU is the only activation the reference has; no biases."""
+(src/model.cpp:162-164).  SiLU is the only activation the reference has; no biases.
+``activation="gelu_tanh"`` makes it ``h = gelu_tanh(xn Wg^T) * (xn Wu^T)`` with ``gelu_tanh(z) = 0.5 z (1
++ tanh(sqrt(2 / pi) (z + 0.044715 z^3)))``."""
 from __future__ import annotations
 
 from typing import Dict, List, Optional
@@ -12,11 +14,17 @@ from ..weights.loader import MATRIX, ParamSpec
 from .base import FeedForward, StepContext, register_feed_forward
 
 
+ACTIVATIONS = ("silu", "gelu_tanh")
+
+
 class SwiGLU(FeedForward):
     graph_safe = True  # kernels only: a step through this part can be captured
 
     def __init__(self, width: int, intermediate: int, names=("gate_proj", "up_proj", "down_proj"),
-                 suffix: str = ".weight"):
+                 suffix: str = ".weight", activation: str = "silu"):
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: activation {activation!r} (known: {', '.join(ACTIVATIONS)})")
+        self.activation = activation
         self.width, self.intermediate = width, intermediate
         self.names = names
         self.suffix = suffix  # what follows a matrix's name in the checkpoint
@@ -43,21 +51,30 @@ class SwiGLU(FeedForward):
     def prepare(self, ops) -> None:
         """Kernels that apply SwiGLU in the epilogue of the gate/up product want the two
         matrices interleaved in blocks of 64 rows."""
-        if not self.fused and getattr(ops, "fuses_swiglu", None) and ops.fuses_swiglu(self.width, self.intermediate):
+        if not self.fused and getattr(ops, "fuses_swiglu", None) and ops.fuses_swiglu(self.width, self.intermediate,
+                                                                                      **self._act):
             gate, up = self.w_gate_up[:self.intermediate], self.w_gate_up[self.intermediate:]
             self.w_gate_up = ops.interleave_gate_up(gate, up)
             self.fused = True
+
+    @property
+    def _act(self):
+        # (only an activation other than SiLU is named to the kernels' bindings)
+        return {} if self.activation == "silu" else {"activation": self.activation}
 
     def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, accumulate: bool = True) -> None:
         """``accumulate`` False: the output is written to ``x`` (float32) instead of added to it."""
         ops, n = ctx.ops, ctx.n
         h = ctx.workspace.rows("ffn_h", n, self.intermediate, ctx.act_dtype)
         if self.fused:
-            ops.linear_swiglu(xn, self.w_gate_up, h)
+            ops.linear_swiglu(xn, self.w_gate_up, h, **self._act)
         else:
             gate_up = ctx.workspace.rows("gate_up", n, 2 * self.intermediate, ctx.act_dtype)
             ops.linear(xn, self.w_gate_up, gate_up)
-            ops.swiglu(gate_up, h)
+            if self.activation == "gelu_tanh":
+                ops.glu_gelu(gate_up, h)
+            else:
+                ops.swiglu(gate_up, h)
         ops.linear(h, self.w_down, x, residual=x if accumulate else None)
 
 

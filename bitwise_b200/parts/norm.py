@@ -72,6 +72,18 @@ class LayerNorm(RMSNorm):
             return
         ctx.ops.layernorm(x, self.weight, self.eps, out, None, other.weight, other_out)
 
+    def forward_residual(self, ctx: StepContext, d, x) -> None:
+        """x += norm(d) with the row statistics of the sublayer's output ``d`` (float32); a constant factor on
+        what is added is this norm's ``gain``."""
+        ctx.ops.layernorm_residual(d, self.weight, self.eps, x)
+
+    def forward_residual_then(self, ctx: StepContext, d, x, nxt: "LayerNorm", out) -> None:
+        if type(nxt) is not LayerNorm or nxt.width != self.width:
+            self.forward_residual(ctx, d, x)
+            nxt.forward(ctx, x, out)
+            return
+        ctx.ops.layernorm_residual(d, self.weight, self.eps, x, next_weight=nxt.weight, next_eps=nxt.eps, next_out=out)
+
 
 register_norm("rmsnorm", RMSNorm)
 register_norm("layernorm", LayerNorm)

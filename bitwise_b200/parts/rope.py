@@ -104,4 +104,78 @@ class RotaryEncoding(PositionEncoding):
         return self._device_tables[key]
 
 
+class RampScaling:
+    """A rescaling of the rotary frequencies for contexts beyond the one a model was trained on: pairs that
+    turn fast stay, pairs that turn slowly are divided by ``factor``, a linear ramp over the pair index
+    blends between.  With ``index(t) = dims * ln(original / (2 pi t)) / (2 ln base)`` the ramp runs from
+    ``lo = max(floor(index(fast)), 0)`` to ``hi = min(ceil(index(slow)), dims - 1)``: ``ramp_i = clamp((i - lo)
+    / max(hi - lo, 0.001), 0, 1)`` and the frequency becomes ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``.
+    cos and sin are multiplied by ``gain_coefficient * ln(factor) + 1``."""
+
+    def __init__(self, factor: float, original: float, fast: float, slow: float, gain_coefficient: float = 0.1):
+        if not (factor > 0 and original > 0 and fast > 0 and slow > 0):
+            raise ValueError("a rescaling of rotary frequencies needs positive factor, original, fast and slow")
+        self.factor, self.original, self.fast, self.slow = float(factor), float(original), float(fast), float(slow)
+        self.gain_coefficient = float(gain_coefficient)
+
+    def key(self):
+        return (self.factor, self.original, self.fast, self.slow, self.gain_coefficient)
+
+    def gain(self) -> float:
+        return self.gain_coefficient * math.log(self.factor) + 1.0
+
+    def frequencies(self, dims: int, base: float) -> np.ndarray:
+        """float64 [dims / 2]."""
+        half = dims // 2
+        f = np.array([base ** (-2.0 * i / dims) for i in range(half)], dtype=np.float64)
+
+        def index(turns: float) -> float:
+            return dims * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+        lo = max(math.floor(index(self.fast)), 0)
+        hi = min(math.ceil(index(self.slow)), dims - 1)
+        ramp = np.clip((np.arange(half, dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return f / self.factor * ramp + f * (1.0 - ramp)
+
+
+class HalfRotaryEncoding(RotaryEncoding):
+    """Tables for a rotation whose pair i is made of entries i and i + dims / 2 of the turned part (the
+    kernels are told the layout; the tables are [positions, dims / 2] either way), with an optional
+    :class:`RampScaling`.  Frequencies and angles are formed in 64-bit and rounded once, to the 32-bit
+    tables that the kernels read; the tables carry the scaling's gain."""
+    layout = "half"
+
+    def __init__(self, dims: int, base: float, scaling: Optional[RampScaling] = None, positions: int = 0):
+        if dims % 2 or dims <= 0:
+            raise ValueError(f"rotary encoding needs an even number of turned entries, got {dims}")
+        if not base > 0:
+            raise ValueError("rotary encoding needs a positive base")
+        self.head_dim = dims
+        self.scaling = scaling
+        if scaling is not None:
+            self.freq64 = scaling.frequencies(dims, float(base))
+            self.gain = scaling.gain()
+        else:
+            self.freq64 = np.array([float(base) ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=np.float64)
+            self.gain = 1.0
+        self.inv_freq = self.freq64.astype(np.float32)
+        self._cos = np.empty((0, dims // 2), dtype=np.float32)
+        self._sin = np.empty((0, dims // 2), dtype=np.float32)
+        self._device_tables = {}
+        self._retired = []
+        if positions:
+            self.reserve(positions)
+
+    def reserve(self, positions: int) -> None:
+        have = self._cos.shape[0]
+        if positions <= have:
+            return
+        angles = np.arange(have, positions, dtype=np.float64)[:, None] * self.freq64[None, :]
+        self._cos = np.concatenate([self._cos, (np.cos(angles) * self.gain).astype(np.float32)], 0)
+        self._sin = np.concatenate([self._sin, (np.sin(angles) * self.gain).astype(np.float32)], 0)
+        self._retired.append(self._device_tables)  # captured graphs may still read the old tables
+        self._device_tables = {}
+
+
 register_position_encoding("rotary", RotaryEncoding)
+register_position_encoding("rotary_half", HalfRotaryEncoding)

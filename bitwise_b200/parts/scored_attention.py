@@ -9,7 +9,8 @@ Before the scores, each on or off by a constructor argument:
 * a short causal convolution over time on every channel of q, k and v, directly after the
   projection: ``y_t = sum_j w[:, j] * u_(t - taps + 1 + j)``, zeros before the sequence's start.
   The last ``taps - 1`` projected rows of a request are its state, kept in a state slot;
-* a root-mean-square norm of every head of q and of k, with one weight of the head's size each;
+* a root-mean-square norm of every head of q and of k, with one weight of the head's size each
+  (``qk_norm="unit"``: without weights, the head is only divided by its root mean square);
 * a rotation of the first ``rot_dims`` entries of every head of q and k: entries 2i and 2i + 1
   form pair i, turned by ``pos * base ** (-2i / rot_dims)`` (tables from a ``RotaryEncoding``).
 
@@ -22,6 +23,9 @@ On the scores ``s = (q . k) * scale``:
   with ``keep_first`` also the keys ``j < keep_first``, at their true distance;
 * ``sink``: one is added to the softmax's denominator (a key of score 0 that has no value);
   ``sink="learned"``: ``exp(sink_h)`` with a learned number per head instead.
+
+``gate`` ("entry" or "head"): the heads' outputs are multiplied by the sigmoid of a projection of the
+mixer's input, per entry or per head, before the output projection (:class:`OutputGate`).
 
 ``values_are_keys``: there is no value projection and nothing but the keys is cached; the
 weighted sum runs over the keys as projected.  ``shares_cache``: the layer has no key and value
@@ -40,6 +44,7 @@ import torch
 
 from ..weights.loader import KEEP32, MATRIX, ParamSpec
 from .base import Mixer, PagedKVNeed, PagedKVView, PositionEncoding, SlotStateNeed, StepContext, register_mixer
+from .gate import OutputGate
 
 
 def distance_slopes(heads: int, exponent: float = 8.0) -> List[float]:
@@ -51,14 +56,14 @@ class ScoredAttention(Mixer):
     graph_safe = True  # kernels only; launches depend on the step's sizes and ctx.max_keys
 
     NAMES = {"q": "q", "k": "k", "v": "v", "out": "o", "conv": ".conv", "norm": ".norm", "bias": ".b", "vmix": "vmix",
-             "dist_a": "r1", "dist_b": "r2", "sink": "sink"}
+             "dist_a": "r1", "dist_b": "r2", "sink": "sink", "gate": "g"}
 
     def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, eps: float = 1e-6,
                  conv_taps: int = 0, qk_norm: bool = False, position: Optional[PositionEncoding] = None, rot_dims: int = 0,
                  softcap: Optional[float] = None, sink: bool = False, slopes: Optional[Sequence[float]] = None,
                  window: Optional[int] = None, values_are_keys: bool = False, shares_cache: bool = False,
                  names: Optional[Dict[str, str]] = None, bias: bool = False, distance_log: bool = False,
-                 keep_first: int = 0, value_mix: Optional[str] = None):
+                 keep_first: int = 0, value_mix: Optional[str] = None, gate: Optional[str] = None):
         if heads % kv_heads:
             raise ValueError(f"{heads} heads are not a multiple of {kv_heads} key/value heads")
         if values_are_keys and vdim != dim:
@@ -74,7 +79,8 @@ class ScoredAttention(Mixer):
         self.width, self.heads, self.kv_heads, self.dim, self.vdim = width, heads, kv_heads, dim, vdim
         self.scale, self.eps = float(scale), float(eps)
         self.taps = int(conv_taps or 0)  # 0: no convolution; 1: a factor per channel and no state
-        self.qk_norm, self.position, self.rot_dims = qk_norm, position, rot_dims
+        self.qk_norm, self.position, self.rot_dims = bool(qk_norm), position, rot_dims
+        self.unit_norm = qk_norm == "unit"  # no weights: a head is divided by its root mean square and no more
         self.softcap, self.sink, self.window = softcap, bool(sink), window
         self.learned_sink = sink == "learned"
         self.bias, self.distance_log, self.value_mix = bool(bias), bool(distance_log), value_mix
@@ -88,6 +94,7 @@ class ScoredAttention(Mixer):
         self.cols = self.q_cols + self.k_cols + self.v_cols
         self.w_in = self.w_o = self.conv_w = self.conv_wt = self.q_norm = self.k_norm = self.slopes = None
         self.b_in = self.dist_a = self.dist_b = self.sinks = self.vmix = None
+        self.gate = OutputGate(width, heads, vdim, gate, self.names["gate"]) if gate else None
 
     # -- what the cache keeps --------------------------------------------------------------
     def cache_need(self):
@@ -127,7 +134,7 @@ class ScoredAttention(Mixer):
                 specs.append(ParamSpec(f"{prefix}.{name}{n['bias']}", (cols,), KEEP32))
             if self.taps:
                 specs.append(ParamSpec(f"{prefix}.{name}{n['conv']}", (cols, self.taps), KEEP32))
-            if self.qk_norm and normed:
+            if self.qk_norm and normed and not self.unit_norm:
                 specs.append(ParamSpec(f"{prefix}.{name}{n['norm']}", (size,), KEEP32, init="ones"))
         if self.value_mix:  # (the first such layer has the tensor too and no use for it)
             specs.append(ParamSpec(f"{prefix}.{n['vmix']}", (), KEEP32, optional=self.value_mix == "source"))
@@ -136,6 +143,8 @@ class ScoredAttention(Mixer):
                       ParamSpec(f"{prefix}.{n['dist_b']}", (self.heads,), KEEP32, init="positive")]
         if self.learned_sink:
             specs.append(ParamSpec(f"{prefix}.{n['sink']}", (self.heads,), KEEP32))
+        if self.gate is not None:
+            specs += self.gate.param_specs(prefix)
         specs.append(ParamSpec(f"{prefix}.{n['out']}", (self.width, self.heads * self.vdim), MATRIX))
         return specs
 
@@ -147,9 +156,14 @@ class ScoredAttention(Mixer):
         if self.taps:
             self.conv_w = torch.cat([state[f"{prefix}.{name}{n['conv']}"] for name, _, _, _ in proj], 0).contiguous()
             self.conv_wt = self.conv_w.t().contiguous()  # [taps, channels]: four channels of a tap lie together
-        if self.qk_norm:
+        if self.unit_norm:
+            ones = torch.ones(self.dim, dtype=torch.float32, device=ws[0].device)
+            self.q_norm, self.k_norm = ones, None if self.shares_cache else ones
+        elif self.qk_norm:
             self.q_norm = state[f"{prefix}.{n['q']}{n['norm']}"]
             self.k_norm = None if self.shares_cache else state[f"{prefix}.{n['k']}{n['norm']}"]
+        if self.gate is not None:
+            self.gate.load_params(state, prefix)
         self.w_o = state[f"{prefix}.{n['out']}"]
         if self.bias:
             self.b_in = torch.cat([state[f"{prefix}.{name}{n['bias']}"] for name, _, _, _ in proj], 0).contiguous()
@@ -163,9 +177,11 @@ class ScoredAttention(Mixer):
             self.slopes = torch.tensor(self.slopes_host, dtype=torch.float32, device=self.w_o.device)
 
     def param_bytes(self) -> int:
-        ts = (self.w_in, self.w_o, self.conv_w, self.q_norm, self.k_norm, self.b_in, self.vmix, self.dist_a, self.dist_b,
+        ts = (self.w_in, self.w_o, self.conv_w, None if self.unit_norm else self.q_norm,
+              None if self.unit_norm else self.k_norm, self.b_in, self.vmix, self.dist_a, self.dist_b,
               self.sinks)  # (the transposed taps are a copy)
-        return sum(t.numel() * t.element_size() for t in ts if t is not None)
+        return sum(t.numel() * t.element_size() for t in ts if t is not None) + (
+            self.gate.param_bytes() if self.gate is not None else 0)
 
     # -- one step --------------------------------------------------------------------------
     def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, cache: PagedKVView,
@@ -198,6 +214,8 @@ class ScoredAttention(Mixer):
         ops.scored_attention(q, cache.k, cache.v, cache.block_table, mixed, self.heads, self.kv_heads, self.dim, self.vdim,
                              self.scale, self.softcap or 0.0, self.sink, self.slopes, self.window or 0, ctx,
                              dist_a=self.dist_a, dist_b=self.dist_b, sinks=self.sinks, keep_first=self.keep_first)
+        if self.gate is not None:
+            self.gate.apply(ctx, xn, mixed)
         ops.linear(mixed, self.w_o, x, residual=x if accumulate else None)
 
 

@@ -204,7 +204,13 @@ class CpuOps:
     def grouped_linear(self, x, w, out, rows, x_group_cols=0, o_group_cols=0, lists=None, order_div=1, gather=True,
                        sorted_x=None):
         if lists is None:
-            raise NotImplementedError("the stand-in runs products over lists only")
+            # one product per group over the same rows: group g reads the columns g * x_group_cols .. + k of x
+            # and writes the columns g * o_group_cols .. + n of out (w: [groups, n, k])
+            groups, n_out, k = w.shape
+            for g in range(groups):
+                src = x[:rows, g * x_group_cols:g * x_group_cols + k].float()
+                out[:rows, g * o_group_cols:g * o_group_cols + n_out] = (src @ w[g].float().t()).to(out.dtype)
+            return
         order = lists[2].reshape(-1)
         for i in range(rows):
             src = x[int(order[i]) // order_div] if gather else x[i]
@@ -248,8 +254,91 @@ class CpuOps:
             y = residual + y
         out.copy_(y.to(out.dtype))
 
-    def fuses_swiglu(self, width, intermediate):
+    def fuses_swiglu(self, width, intermediate, activation="silu"):
         return False
+
+    # -- layer norm, latent attention and the element-wise steps of gated designs ---------------------
+    @staticmethod
+    def _layer_normed(t, eps):
+        c = t - t.mean(-1, keepdim=True)
+        return c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps)
+
+    def layernorm(self, x, weight, eps, out, rows=None, weight2=None, out2=None):
+        src = x if rows is None else x[rows.long()]
+        n = self._layer_normed(src.float(), eps)
+        out.copy_((n * weight).to(out.dtype))
+        if out2 is not None:
+            out2.copy_((n * weight2).to(out2.dtype))
+
+    def layernorm_residual(self, d, weight, eps, x, next_weight=None, next_eps=0.0, next_out=None):
+        x += self._layer_normed(d, eps) * weight
+        if next_out is not None:
+            self.layernorm(x, next_weight, next_eps, next_out)
+
+    @staticmethod
+    def _turn(t, p, cos, sin, half_layout):
+        """t: [n, ..., size]; the first 2 * pairs entries turn by the tables' rows p."""
+        if cos is None:
+            return t
+        pairs = cos.shape[1]
+        shape = (t.shape[0],) + (1,) * (t.dim() - 2) + (pairs,)
+        c, s = cos[p].reshape(shape), sin[p].reshape(shape)
+        out = t.clone()
+        if half_layout:
+            a, b = t[..., :pairs], t[..., pairs:2 * pairs]
+            out[..., :pairs], out[..., pairs:2 * pairs] = a * c - b * s, b * c + a * s
+        else:
+            a, b = t[..., 0:2 * pairs:2], t[..., 1:2 * pairs:2]
+            out[..., 0:2 * pairs:2], out[..., 1:2 * pairs:2] = a * c - b * s, b * c + a * s
+        return out
+
+    def latent_store(self, d, weight, eps, pos, row_seq, cos, sin, block_table, cache, rank, rot_dim, half_layout=False):
+        page = cache.shape[1]
+        p = pos.long()
+        c = d[:, :rank]
+        c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * weight
+        kr = self._turn(d[:, rank:rank + rot_dim], p, cos, sin, half_layout)
+        for r in range(d.shape[0]):
+            blk = int(block_table[int(row_seq[r]), int(p[r]) // page])
+            cache[blk, int(p[r]) % page] = torch.cat([c[r], kr[r]]).to(cache.dtype)
+
+    def rotate_heads(self, q, heads, head_stride, offset, rot_dim, out, out_head_stride, out_offset, pos, cos, sin,
+                     half_layout=False):
+        n = q.shape[0]
+        src = q.float().reshape(n, -1)[:, :heads * head_stride].reshape(n, heads, head_stride)[..., offset:offset + rot_dim]
+        turned = self._turn(src, pos.long(), cos, sin, half_layout)
+        dst = out.reshape(n, -1)[:, :heads * out_head_stride].reshape(n, heads, out_head_stride)
+        dst[..., out_offset:out_offset + rot_dim] = turned.to(out.dtype)
+
+    def latent_attention_tile_heights(self, heads, rank, rot_dim):
+        return [max(1, 32 // heads)]
+
+    def latent_attention(self, q, cache, block_table, out, heads, rank, rot_dim, scale, ctx, window=0, sinks=None):
+        page = cache.shape[1]
+        dk = rank + rot_dim
+        for r in range(q.shape[0]):
+            p = int(ctx.pos[r])
+            idx = torch.arange(max(0, p - window + 1) if window else 0, p + 1)
+            keys = cache[block_table[int(ctx.row_seq[r])][(idx // page).long()].long(), (idx % page).long()].float()
+            s = (q[r].float().view(heads, dk) @ keys.t()) * scale
+            m = s.max(-1, keepdim=True).values
+            if sinks is not None:
+                m = torch.maximum(m, sinks.view(-1, 1))
+            e = torch.exp(s - m)
+            den = e.sum(-1, keepdim=True) + (torch.exp(sinks.view(-1, 1) - m) if sinks is not None else 0.0)
+            out[r] = ((e / den) @ keys[:, :rank]).reshape(-1).to(out.dtype)
+
+    def sigmoid_gate(self, v, g, group=1):
+        v.copy_((v.float() * torch.sigmoid(g.float()).repeat_interleave(group, dim=1)).to(v.dtype))
+
+    def glu_gelu(self, gate_up, out):
+        inter = out.shape[1]
+        g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+        gelu = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))
+        out.copy_((gelu * u).to(out.dtype))
+
+    def softcap_rows(self, z, cap):
+        z.copy_(cap * torch.tanh(z / cap))
 
     def rope_cache(self, qkv, pos, row_seq, cos, sin, block_table, kcache, vcache, heads, kv_heads, head_dim,
                    write_kv=True):

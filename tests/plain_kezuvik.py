@@ -19,11 +19,31 @@ is a dict name -> tensor; ``cfg`` is the model's config.json as a dict.
 * a layer is ``x += m * post1(mixer(pre1(x)))``, ``x += m * post2(ff(pre2(x)))``, all four layer norms
 * the logits are capped by ``cap * tanh(z / cap)``
 """
+import contextlib
 import math
 
 import torch
 
 F64 = torch.float64
+
+_ROUND = None
+
+
+@contextlib.contextmanager
+def rounding(fn):
+    """Inside the block, what the serving precision stores in 16 bits between its kernels (the sublayers' inputs,
+    projections, cached vectors, the heads' outputs) is passed through ``fn``: the plain result then shows how large
+    an error rounding alone causes."""
+    global _ROUND
+    _ROUND, old = fn, _ROUND
+    try:
+        yield
+    finally:
+        _ROUND = old
+
+
+def stored(x):
+    return _ROUND(x) if _ROUND is not None else x
 
 
 def layer_norm(x, g, eps):
@@ -107,12 +127,12 @@ def latent_mixer(h, w, pre, m, eps, positions, second):
     """``second``: the kind with rescaled frequencies, a sink per head and a gate per head."""
     n = h.shape[0]
     H, dim, rd, vd, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    cq = unit_rms(h @ w[pre + "dq"].T, eps) * w[pre + "dq.norm"]
-    q = (cq @ w[pre + "uq"].T).reshape(n, H, dim + rd)
+    cq = stored(unit_rms(h @ w[pre + "dq"].T, eps) * w[pre + "dq.norm"])
+    q = stored(cq @ w[pre + "uq"].T).reshape(n, H, dim + rd)
     d = h @ w[pre + "dkv"].T
-    c = unit_rms(d[:, :rank], eps) * w[pre + "dkv.norm"]
-    k_rot = rotate_half(d[:, rank:], positions, m["rot"])
-    q_rot = rotate_half(q[:, :, dim:], positions, m["rot"])
+    c = stored(unit_rms(d[:, :rank], eps) * w[pre + "dkv.norm"])
+    k_rot = stored(rotate_half(d[:, rank:], positions, m["rot"]))
+    q_rot = stored(rotate_half(q[:, :, dim:], positions, m["rot"]))
     k = (c @ w[pre + "uk"].T).reshape(n, H, dim)
     v = (c @ w[pre + "uv"].T).reshape(n, H, vd)
     scores = (torch.einsum("ihd,jhd->hij", q[:, :, :dim], k) + torch.einsum("ihd,jd->hij", q_rot, k_rot)) * m["scale"]
@@ -121,7 +141,7 @@ def latent_mixer(h, w, pre, m, eps, positions, second):
     p = softmax_rows(scores, visible, w[pre + "sink"] if second else None)
     o = torch.einsum("hij,jhd->ihd", p, v)
     g = torch.sigmoid(h @ w[pre + "g"].T)
-    o = o * (g[:, :, None] if second else g.reshape(n, H, vd))
+    o = stored(stored(o) * (g[:, :, None] if second else g.reshape(n, H, vd)))
     return o.reshape(n, H * vd) @ w[pre + "o"].T
 
 
@@ -133,9 +153,9 @@ def window_mixer(h, w, pre, m, eps, positions):
         u = h @ w[pre + name].T + w[pre + name + ".b"]
         return causal_conv(u, w[pre + name + ".conv"]) if m.get("conv") else u
 
-    q = unit_rms(project("q").reshape(n, H, dim), eps)
-    k = unit_rms(project("k").reshape(n, G, dim), eps)
-    v = project("v").reshape(n, G, vd)
+    q = stored(unit_rms(project("q").reshape(n, H, dim), eps))
+    k = stored(unit_rms(project("k").reshape(n, G, dim), eps))
+    v = stored(project("v").reshape(n, G, vd))
     rep = H // G
     k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
     scores = torch.einsum("ihd,jhd->hij", q, k) * m["scale"]
@@ -145,34 +165,34 @@ def window_mixer(h, w, pre, m, eps, positions):
     if m.get("mask"):
         visible = visible & (dist < m["mask"]["size"])
     p = softmax_rows(scores, visible[None].expand(H, n, n))
-    o = torch.einsum("hij,jhd->ihd", p, v).reshape(n, H * vd)
-    return (o * torch.sigmoid(h @ w[pre + "g"].T)) @ w[pre + "o"].T
+    o = stored(torch.einsum("hij,jhd->ihd", p, v).reshape(n, H * vd))
+    return stored(o * torch.sigmoid(h @ w[pre + "g"].T)) @ w[pre + "o"].T
 
 
 def dense_ff(h, w, pre):
-    return (gelu_tanh(h @ w[pre + "gate"].T) * (h @ w[pre + "up"].T)) @ w[pre + "down"].T
+    return stored(gelu_tanh(stored(h @ w[pre + "gate"].T)) * stored(h @ w[pre + "up"].T)) @ w[pre + "down"].T
 
 
 def forward(cfg, weights, tokens, layers_out=None):
     """Logits [tokens, vocab] of one whole sequence; ``layers_out``: a list that receives the stream after
     every layer."""
     w = {k: v.to(F64) for k, v in weights.items() if v.dtype != torch.int32}
-    eps, mult = cfg["norm"]["eps"], cfg["residual_mult"]
+    eps, mult = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
     positions = list(range(len(tokens)))
     x = w["embed"][torch.as_tensor(tokens)]
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
-        h = layer_norm(x, w[p + "norm1"], eps)
+        h = stored(layer_norm(x, w[p + "norm1"], eps))
         if layer["type"] == "attention":
             y = window_mixer(h, w, p + "mix.", layer["mixer"], eps, positions)
         else:
             y = latent_mixer(h, w, p + "mix.", layer["mixer"], eps, positions, layer["type"] == "latent_attention_2")
         x = x + mult * layer_norm(y, w[p + "norm1b"], eps)
         if layer.get("mlp"):
-            y = dense_ff(layer_norm(x, w[p + "norm2"], eps), w, p + "mlp.")
+            y = dense_ff(stored(layer_norm(x, w[p + "norm2"], eps)), w, p + "mlp.")
             x = x + mult * layer_norm(y, w[p + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
-    z = layer_norm(x, w["final.norm"], eps) @ w["embed"].T
+    z = stored(layer_norm(x, w["final.norm"], eps)) @ w["embed"].T
     cap = cfg.get("logit_softcap")
     return cap * torch.tanh(z / cap) if cap else z

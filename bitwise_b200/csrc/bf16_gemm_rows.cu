@@ -103,7 +103,7 @@ struct RopeCache {
 template <int EPI, bool ROWS16, int NT>
 __global__ void __launch_bounds__(NT * kWarps * 32)
 linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* Y,
-                   const float* residual, int M, int N, int K, int tiles, RopeCache rc, int* failure) {
+                   const float* residual, int M, int N, int K, int tiles, RopeCache rc, int* failure, int act) {
   static_assert(EPI != 3 || NT == 2, "a rotation needs both halves of a head in the tile");
   constexpr int R = ROWS16 ? 16 : 8;
   constexpr int kItemBytes = kGroupBytes;  // what a warp fetches per (tile, chunk): its group's 8 rows
@@ -305,7 +305,7 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         const float g = __bfloat162float(__float2bfloat16_rn(chunk_sum(0, r, j)));
         const float u = __bfloat162float(__float2bfloat16_rn(chunk_sum(1, r, j)));
         static_cast<__nv_bfloat16*>(Y)[static_cast<size_t>(r) * inter + tile * 8 + j] =
-            __float2bfloat16_rn(bw::swiglu_one(g, u));
+            __float2bfloat16_rn(bw::glu_one(g, u, act));
       }
     } else {
 #pragma unroll
@@ -403,7 +403,7 @@ bool rows_shape(int m, int n, int k, bool swiglu, RowsShape* s) {
 
 template <int EPI, bool ROWS16, int NT>
 int launch_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, const float* residual, int m, int n, int k,
-                const RowsShape& s, cudaStream_t stream, const RopeCache& rc = RopeCache{}) {
+                const RowsShape& s, cudaStream_t stream, const RopeCache& rc = RopeCache{}, int act = 0) {
   auto kernel = linear_rows_kernel<EPI, ROWS16, NT>;
   static bool configured = false;
   if (!configured) {
@@ -422,16 +422,16 @@ int launch_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, const f
   int* word = bw::failure_word();
   if (!word) return -1;
   bw::launch_pdl(kernel, dim3(s.grid), dim3(NT * kWarps * 32), s.smem, stream, map_x, map_w, y, residual, m, n, k, s.tiles, rc,
-                 word);
+                 word, act);
   return bw::launch_status();
 }
 
 template <int EPI>
 int launch_rows_epi(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, const float* residual, int m, int n, int k,
-                    const RowsShape& s, cudaStream_t stream) {
+                    const RowsShape& s, cudaStream_t stream, int act = 0) {
   if (s.nt == 2)
-    return s.rows16 ? launch_rows<EPI, true, 2>(x, w, y, residual, m, n, k, s, stream)
-                    : launch_rows<EPI, false, 2>(x, w, y, residual, m, n, k, s, stream);
+    return s.rows16 ? launch_rows<EPI, true, 2>(x, w, y, residual, m, n, k, s, stream, RopeCache{}, act)
+                    : launch_rows<EPI, false, 2>(x, w, y, residual, m, n, k, s, stream, RopeCache{}, act);
   if (EPI == 1) return -1;  // SwiGLU tiles always hold two groups
   return s.rows16 ? launch_rows<EPI == 1 ? 0 : EPI, true, 1>(x, w, y, residual, m, n, k, s, stream)
                   : launch_rows<EPI == 1 ? 0 : EPI, false, 1>(x, w, y, residual, m, n, k, s, stream);
@@ -455,17 +455,20 @@ BW_API int bw_bf16_linear_rows_usable(const void* x, const void* w, int m, int n
          (!swiglu || n % 128 == 0) && rows_shape(m, n, k, swiglu != 0, &s) && rows_encoder() != nullptr;
 }
 
-// y_kind 0: y bfloat16 [m][n].  1: SwiGLU of interleaved gate/up weights, y bfloat16 [m][n / 2].
+// y_kind 0: y bfloat16 [m][n].  1: SwiGLU of interleaved gate/up weights, y bfloat16 [m][n / 2];
+// 1 + 4 * act: the same step with the gate's activation `act` (bw::glu_one).
 // 2: y float32 [m][n] = (residual +) product; y may alias residual.
 BW_API int bw_bf16_linear_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_kind, const float* residual,
                                int m, int n, int k, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
   RowsShape s;
+  const int act = (y_kind & 3) == 1 ? y_kind >> 2 : 0;
+  if ((y_kind & 3) == 1) y_kind = 1;
   if (!bw_bf16_linear_rows_usable(x, w, m, n, k, y_kind == 1) || !rows_shape(m, n, k, y_kind == 1, &s)) {
     bw::set_error("linear (few rows): shape [%d x %d] x [%d x %d] is not for this path", m, k, n, k);
     return -1;
   }
-  if (y_kind == 1) return launch_rows_epi<1>(x, w, y, nullptr, m, n, k, s, stream);
+  if (y_kind == 1) return launch_rows_epi<1>(x, w, y, nullptr, m, n, k, s, stream, act);
   if (y_kind == 2) return launch_rows_epi<2>(x, w, y, residual, m, n, k, s, stream);
   return launch_rows_epi<0>(x, w, y, nullptr, m, n, k, s, stream);
 }

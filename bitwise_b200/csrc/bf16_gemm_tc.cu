@@ -297,7 +297,7 @@ __device__ __forceinline__ float ordered_chunk_sum(const float* __restrict__ par
 // gate at column 128 (c / 64) + c % 64 and the up value 64 columns further. Gate and up are
 // rounded to bfloat16 first, as if the product had been stored, then combined.
 __global__ void reduce_swiglu_kernel(const float* __restrict__ partials, int num_chunks, __nv_bfloat16* __restrict__ H,
-                                     int M, int N) {
+                                     int M, int N, int act) {
   bw::pdl_enter();
   const int inter = N / 2;
   const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
@@ -307,12 +307,14 @@ __global__ void reduce_swiglu_kernel(const float* __restrict__ partials, int num
   const size_t og = static_cast<size_t>(r) * N + 128 * (c / 64) + (c % 64);
   const float g = __bfloat162float(__float2bfloat16_rn(ordered_chunk_sum(partials, num_chunks, plane, og)));
   const float u = __bfloat162float(__float2bfloat16_rn(ordered_chunk_sum(partials, num_chunks, plane, og + 64)));
-  H[idx] = __float2bfloat16_rn(bw::swiglu_one(g, u));
+  H[idx] = __float2bfloat16_rn(bw::glu_one(g, u, act));
 }
 
 // EPI 0: y = product in bfloat16.  EPI 2: y = (residual +) product in float32.  EPI 1 (whole
 // mode only): the product is the interleaved gate/up projection and y[m][n / 2] = SwiGLU of it
-// (bfloat16). In split mode the kernel writes chunk sums and the second kernel finishes.
+// (bfloat16), or the same step with another activation on the gate: with EPI 1 the argument
+// `y_is_f32` names the activation (bw::glu_one). In split mode the kernel writes chunk sums and the
+// second kernel finishes.
 //
 // A wide tile has no path for pieces that are cut by the matrix edge or that do not start on
 // 32 bytes (the path costs registers that the totals need): the host gives wide tiles only
@@ -651,7 +653,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const float g1 = __bfloat162float(__float2bfloat16_rn(total[j + 2 * e + 1]));
             const float u0 = __bfloat162float(__float2bfloat16_rn(total[PW + j + 2 * e]));
             const float u1 = __bfloat162float(__float2bfloat16_rn(total[PW + j + 2 * e + 1]));
-            o[e] = pack_bf16(bw::swiglu_one(g0, u0), bw::swiglu_one(g1, u1));
+            o[e] = pack_bf16(bw::glu_one(g0, u0, y_is_f32), bw::glu_one(g1, u1, y_is_f32));
           }
           if (wide_store) {
             st256(out + j, o);
@@ -884,6 +886,7 @@ namespace {
 // What follows the product: nothing, or SwiGLU.
 struct Fused {
   int mode = 0;  // 0 none, 2 swiglu (y is [m][n / 2] bfloat16)
+  int act = 0;   // mode 2: the gate's activation (bw::glu_one)
 };
 
 // Once per device and kernel variant: the shared-memory limit of the kernel is raised and, for
@@ -965,7 +968,7 @@ int launch_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_
     const size_t outputs = static_cast<size_t>(m) * n;
     if (fused.mode == 2)
       bw::launch_pdl(reduce_swiglu_kernel, dim3(static_cast<unsigned>((outputs / 2 + 255) / 256)), dim3(256), 0, stream, 
-          partials, chunks, static_cast<__nv_bfloat16*>(y), m, n);
+          partials, chunks, static_cast<__nv_bfloat16*>(y), m, n, fused.act);
     else
       bw::launch_pdl(reduce_chunks_kernel, dim3(static_cast<unsigned>((outputs + 255) / 256)), dim3(256), 0, stream, partials, chunks, y,
                                                                                             y_is_f32, residual, m, n);
@@ -1089,20 +1092,24 @@ BW_API int bw_bf16_linear_tc_grouped(const __nv_bfloat16* x, const __nv_bfloat16
 }
 
 // h[m][n / 2] = SwiGLU of x W^T for gate/up weights interleaved in blocks of 64 rows
-// (n a multiple of 128).
+// (n a multiple of 128). act: the gate's activation, 0 SiLU, 1 the tanh form of GELU.
 BW_API int bw_bf16_linear_tc_swiglu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* h, int m, int n, int k,
-                                    float* partials, cudaStream_t stream) {
+                                    float* partials, int act, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
+  if (act != bw::kGluSilu && act != bw::kGluGeluTanh) {
+    bw::set_error("linear + gated activation: unknown activation %d", act);
+    return -1;
+  }
   if (n % 128 || !bw_bf16_linear_tc_usable(x, w, k)) {
     bw::set_error("linear + SwiGLU: needs n %% 128 == 0 (got %d) and rows that start on 16 bytes", n);
     return -1;
   }
-  if (rows_path_takes(m, n, k, 1, x, w)) return bw_bf16_linear_rows(x, w, h, 1, nullptr, m, n, k, stream);
+  if (rows_path_takes(m, n, k, 1, x, w)) return bw_bf16_linear_rows(x, w, h, 1 + 4 * act, nullptr, m, n, k, stream);
   int* word = bw::failure_word();
   if (!word) return -1;
   Fused f;
-  f.mode = 2;
-  return launch_tc_rows<1>(x, w, h, 0, nullptr, m, n, k, word, partials, f, stream);
+  f.mode = 2, f.act = act;
+  return launch_tc_rows<1>(x, w, h, act, nullptr, m, n, k, word, partials, f, stream);
 }
 
 // ---------------------------------------------------------------------------------------

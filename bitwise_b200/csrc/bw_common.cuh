@@ -204,6 +204,21 @@ __device__ __forceinline__ float swiglu_one(float g, float u) {
   return __fmul_rn(__fmul_rn(g, sig), u);
 }
 
+// The same step with the tanh form of GELU on the gate: gelu_tanh(g) * u, gelu_tanh(z) = 0.5 z (1 + tanh(y)),
+// y = sqrt(2 / pi) (z + 0.044715 z^3). 0.5 (1 + tanh(y)) is sigmoid(2 y), which keeps its relative accuracy
+// where tanh(y) is near -1; the hardware's exp and reciprocal as above.
+__device__ __forceinline__ float geglu_one(float g, float u) {
+  const float y = __fmul_rn(0.7978845608028654f, __fmaf_rn(__fmul_rn(0.044715f, __fmul_rn(g, g)), g, g));
+  const float sig = __fdividef(1.0f, __fadd_rn(1.0f, __expf(__fmul_rn(-2.0f, y))));
+  return __fmul_rn(__fmul_rn(g, sig), u);
+}
+
+// The gated feed-forward's inner step by the gate's activation: 0 SiLU, 1 the tanh form of GELU.
+constexpr int kGluSilu = 0, kGluGeluTanh = 1;
+__device__ __forceinline__ float glu_one(float g, float u, int act) {
+  return act == kGluGeluTanh ? geglu_one(g, u) : swiglu_one(g, u);
+}
+
 // The tail of RMSNorm for one element, and the scale from the sum of squares: one definition
 // for the stand-alone kernel and the fused one.
 __device__ __forceinline__ float rms_scale(float sumsq, int width, float eps) {

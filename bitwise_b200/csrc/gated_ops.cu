@@ -38,7 +38,12 @@ __global__ void glu_gelu_kernel(const act_t* __restrict__ gate_up, act_t* __rest
   const size_t r = i / inter;
   const int c = static_cast<int>(i - r * inter);
   const act_t* g = gate_up + r * 2 * inter + c;
+#if BW_ACT_BF16
+  // the serving precision's form, shared with the epilogue of the gate/up product: both give the same bits
+  out[i] = bw::from_f<act_t>(bw::geglu_one(bw::to_f(g[0]), bw::to_f(g[inter])));
+#else
   out[i] = bw::from_f<act_t>(__fmul_rn(gelu_tanh_f(bw::to_f(g[0])), bw::to_f(g[inter])));
+#endif
 }
 
 __global__ void softcap_rows_kernel(float* z, float cap, size_t count) {

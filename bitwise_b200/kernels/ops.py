@@ -59,7 +59,7 @@ class KernelOps:
     """Operations of one precision.  ``act_dtype`` is the dtype of activations between
     kernels (the residual stream, logits and norm weights are float32 in both)."""
 
-    FUSED_ACTIVATIONS = ("silu",)  # what the gate/up product can apply in its epilogue
+    FUSED_ACTIVATIONS = ("silu", "gelu_tanh")  # what the gate/up product can apply in its epilogue, by index
 
     def __init__(self, dtype: str, verbose_build: bool = True):
         if dtype not in ("float32", "bfloat16"):
@@ -229,9 +229,12 @@ class KernelOps:
         u = up.reshape(inter // 64, 64, k)
         return torch.stack([g, u], dim=1).reshape(2 * inter, k).contiguous()
 
-    def linear_swiglu(self, x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor) -> None:
-        """out[m][i] = silu(x @ gate_i) * (x @ up_i) for interleaved gate/up weights; gate and
-        up are rounded to act_dtype before they are combined, as if they had been stored."""
+    def linear_swiglu(self, x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor,
+                      activation: str = "silu") -> None:
+        """out[m][i] = act(x @ gate_i) * (x @ up_i) for interleaved gate/up weights, act SiLU or the tanh form
+        of GELU; gate and up are rounded to act_dtype before they are combined, as if they had been stored."""
+        if activation not in self.FUSED_ACTIVATIONS:
+            raise KernelError(f"linear_swiglu: activation {activation!r}")
         m, k = x.shape
         n = w_interleaved.shape[0]
         _need(x, self.act_dtype, "linear_swiglu x", 2)
@@ -243,7 +246,8 @@ class KernelOps:
         if m <= self._split_rows:
             partials, _ = self._linear_scratch(x.device, n, k)
         self._call("bw_bf16_linear_tc_swiglu", _p(x), _p(w_interleaved), _p(out), _c_int(m), _c_int(n), _c_int(k),
-                   _p(partials), self._stream(), launches=self._linear_kernels(m, n, k, True, partials is not None))
+                   _p(partials), _c_int(self.FUSED_ACTIVATIONS.index(activation)), self._stream(),
+                   launches=self._linear_kernels(m, n, k, True, partials is not None))
 
     def _linear_kernels(self, m: int, n: int, k: int, swiglu: bool, scratch: bool) -> int:
         """Kernels that a product of this shape launches (2 when it is split along k)."""

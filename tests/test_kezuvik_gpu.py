@@ -28,6 +28,10 @@ WEIGHT_SEED = 3
 _models, _plain = {}, {}
 
 
+def to_bf16(a):
+    return a.to(torch.bfloat16).to(F64)
+
+
 def ops_of(dtype):
     from bitwise_b200.kernels.ops import get_ops
     return get_ops(dtype)
@@ -173,6 +177,33 @@ def test_gates_gelu_step_and_cap(dtype):
     assert float(z.abs().max()) <= 7.5
 
 
+@pytest.mark.parametrize("m", [1, 8, 16, 40, 128, 300, 1100])
+@pytest.mark.parametrize("width,inter", [(256, 320), (512, 1408), (64, 64)])
+def test_gelu_in_the_epilogue_of_the_gate_and_up_product(m, width, inter):
+    """The serving precision applies the gated step in the product's epilogue; the bits are those of the product
+    followed by the stand-alone kernel, for steps of few rows, of a tile's rows and of many tiles."""
+    ops = ops_of("bfloat16")
+    assert ops.fuses_swiglu(width, inter, activation="gelu_tanh")
+    g = torch.Generator().manual_seed(m + inter)
+    x = torch.randn(m, width, generator=g).to(torch.bfloat16).to(DEV)
+    gate = (torch.randn(inter, width, generator=g) * 2.0 / math.sqrt(width)).to(torch.bfloat16).to(DEV)
+    up = (torch.randn(inter, width, generator=g) / math.sqrt(width)).to(torch.bfloat16).to(DEV)
+    fused = torch.zeros(m, inter, dtype=torch.bfloat16, device=DEV)
+    ops.linear_swiglu(x, ops.interleave_gate_up(gate, up), fused, activation="gelu_tanh")
+    gate_up = torch.zeros(m, 2 * inter, dtype=torch.bfloat16, device=DEV)
+    ops.linear(x, torch.cat([gate, up]).contiguous(), gate_up)
+    apart = torch.zeros(m, inter, dtype=torch.bfloat16, device=DEV)
+    ops.glu_gelu(gate_up, apart)
+    assert torch.equal(fused, apart)
+    x64 = x.to(F64).cpu()
+    want = P.gelu_tanh(to_bf16(x64 @ gate.to(F64).cpu().T)) * to_bf16(x64 @ up.to(F64).cpu().T)
+    close(fused, want, "bfloat16", "gelu(gate) * up")
+    silu = torch.zeros(m, inter, dtype=torch.bfloat16, device=DEV)
+    ops.linear_swiglu(x, ops.interleave_gate_up(gate, up), silu)          # the other activation is still itself
+    g64 = to_bf16(x64 @ gate.to(F64).cpu().T)
+    close(silu, g64 * torch.sigmoid(g64) * to_bf16(x64 @ up.to(F64).cpu().T), "bfloat16", "silu(gate) * up")
+
+
 def run_latent_attention(ops, dtype, q, cache, table, batch, heads, rank, rot_dim, scale, sinks):
     out = torch.zeros(batch.n, heads * rank, dtype=act(dtype), device=DEV)
     ops.latent_attention(q, cache, table, out, heads, rank, rot_dim, scale, batch, 0, sinks=sinks)
@@ -248,10 +279,6 @@ def model_of(name, dtype):
     if (name, dtype) not in _models:
         _models[(name, dtype)] = Model.from_tensors(CONFIGS[name], random_weights(CONFIGS[name], WEIGHT_SEED), dtype=dtype, device=DEV)
     return _models[(name, dtype)]
-
-
-def to_bf16(a):
-    return a.to(torch.bfloat16).to(F64)
 
 
 def plain_pair(cfg, W, toks, collect=None):

@@ -879,6 +879,215 @@ def compare_sebavik(args, pk):
     line["kernels"] = sebavik_kernel_table(z, pk, args.page)
     return line
 
+# ---- the Kezuvik design beside Favudra at equal size (--compare kezuvik) ------------------------
+KEZUVIK_SIZES = {
+    # width, layers, latent layers: heads x (dim + rot_dim), value size, latents of keys/values and of queries;
+    # window layers: heads on kv_heads of dim, window, taps; ff, vocab
+    "small": dict(width=1024, layers=4, heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256, q_rank=384,
+                  w_heads=8, w_kv_heads=2, w_dim=128, window=512, taps=4, ff=2816, vocab=32768),
+    "medium": dict(width=2048, layers=4, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768,
+                   w_heads=16, w_kv_heads=4, w_dim=128, window=1024, taps=4, ff=5632, vocab=32768),
+}
+
+
+def kezuvik_config(z):
+    """Layers in the order latent attention, window attention, latent attention of the second kind (rescaled rotary
+    frequencies, sinks, a gate per head), window attention, and so on; every layer with a feed-forward."""
+    from bitwise_b200.config import KezuvikConfig, KezuvikLayerConfig, KezuvikMixerConfig, RotScalingConfig
+    layers = []
+    for i in range(z["layers"]):
+        kind = i % 4
+        if kind in (1, 3):
+            m = KezuvikMixerConfig("attention", z["w_heads"], z["w_dim"], z["w_dim"], z["w_dim"] ** -0.5,
+                                   kv_heads=z["w_kv_heads"], conv=z["taps"], window=z["window"])
+        else:
+            m = KezuvikMixerConfig("latent_attention_2" if kind == 2 else "latent_attention", z["heads"], z["dim"], z["vdim"],
+                                   (z["dim"] + z["rot_dim"]) ** -0.5, rot_dim=z["rot_dim"], kv_rank=z["kv_rank"],
+                                   q_rank=z["q_rank"], rot_base=1e6, rot_dims=z["rot_dim"],
+                                   rot_scaling=RotScalingConfig(4.0, 4096.0, 32.0, 1.0) if kind == 2 else None)
+        layers.append(KezuvikLayerConfig(m, z["ff"]))
+    return KezuvikConfig(vocab=z["vocab"], width=z["width"], eps=1e-5, layers=tuple(layers), residual_mult=0.7,
+                         logit_softcap=30.0)
+
+
+def kezuvik_twin(z):
+    """Favudra with the same width, layers, feed-forward and vocabulary and the window layers' heads, key/value heads
+    and head size: full attention (convolution, norm per head, rotation, cap, sink) where Kezuvik has latent attention,
+    window attention where it has window attention."""
+    from bitwise_b200.config import FavudraConfig, FavudraLayerConfig, FavudraMixerConfig
+    H, G, hd = z["w_heads"], z["w_kv_heads"], z["w_dim"]
+    layers = []
+    for i in range(z["layers"]):
+        if i % 2:
+            m = FavudraMixerConfig("attention_2", H, hd, hd, kv_heads=G, scale=hd ** -0.5, window=z["window"])
+        else:
+            m = FavudraMixerConfig("attention", H, hd, hd, kv_heads=G, scale=hd ** -0.5, conv=z["taps"], rot_base=1e6,
+                                   rot_dims=64, softcap=30.0)
+        layers.append(FavudraLayerConfig(m, z["ff"]))
+    return FavudraConfig(vocab=z["vocab"], width=z["width"], eps=1e-5, embedding_scale=z["width"] ** 0.5, logit_scale=0.25,
+                         layers=tuple(layers))
+
+
+def kezuvik_kernel_table(z, pk, page=16):
+    """Every kernel that the design added or changed, alone at the size's shapes, beside the like kernel of an
+    earlier design: milliseconds and the fraction of its roofline (measured copy bandwidth or bf16 peak)."""
+    import torch
+    from bitwise_b200.kernels.ops import get_ops
+    from bitwise_b200.parts.rope import HalfRotaryEncoding, RampScaling, RotaryEncoding
+    from bitwise_b200.parts.scored_attention import SEQUENCE_TILE, distance_slopes
+    ops = get_ops("bfloat16")
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    H, rank, rot, dim, vdim, width = z["heads"], z["kv_rank"], z["rot_dim"], z["dim"], z["vdim"], z["width"]
+    WH, WG, hd, win, taps, ff = z["w_heads"], z["w_kv_heads"], z["w_dim"], z["window"], z["taps"], z["ff"]
+    dk = rank + rot
+    out = {}
+
+    def frac_flops(flops, ms):
+        return round(flops / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 4)
+
+    def frac_bytes(nbytes, ms):
+        return round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+
+    def put(name, ms, frac, twin_ms, twin_frac, bound, twin):
+        out[name] = {"ms": round(ms, 4), "frac": frac, "twin_ms": round(twin_ms, 4), "twin_frac": twin_frac, "bound": bound,
+                     "twin": twin, "gap_ratio": round(twin_frac / frac, 2) if frac else None}
+
+    cos_h, sin_h = HalfRotaryEncoding(rot, 1e6, RampScaling(4.0, 4096.0, 32.0, 1.0), positions=2048).rotary_tables(dev)
+    cos_p, sin_p = RotaryEncoding(rot, 1e6, positions=2048).rotary_tables(dev)
+    cos_f, sin_f = RotaryEncoding(64, 1e6, positions=2048).rotary_tables(dev)
+    slopes = torch.tensor(distance_slopes(WH), dtype=torch.float32, device=dev)
+    sinks = torch.zeros(H, dtype=torch.float32, device=dev)
+    for label, seqs in (("prefill_2048", [(0, 2048)]), ("decode_b8_ctx2048", [(2047, 1)] * 8)):
+        keys = max(p0 + c for p0, c in seqs)
+        blocks = (keys + page - 1) // page
+        nseq = len(seqs)
+        table = torch.arange(nseq * blocks, dtype=torch.int32, device=dev).reshape(nseq, blocks)
+        heights = set(ops.latent_attention_tile_heights(H, rank, rot)) | set(ops.scored_attention_tile_heights(WH // WG, hd, hd)) | {SEQUENCE_TILE}
+        b = KernelBatch(seqs, sorted(heights), dev)
+        b.seq_slot = torch.arange(nseq, dtype=torch.int32, device=dev)
+        n = b.n
+        prefill = n > nseq
+        pairs = sum(c * p0 + c * (c + 1) // 2 for p0, c in seqs)
+        wpairs = sum(sum(min(p + 1, win) for p in range(p0, p0 + c)) for p0, c in seqs)
+        # latent attention with a sink per head beside the same attention without (the Nuderax design's)
+        cache = torch.randn(nseq * blocks + 1, page, dk, device=dev).to(bf)
+        q = torch.randn(n, H * dk, device=dev).to(bf)
+        o = torch.empty(n, H * rank, dtype=bf, device=dev)
+        ms = timed_device(lambda: ops.latent_attention(q, cache, table, o, H, rank, rot, dk ** -0.5, b, sinks=sinks), flush=flush)
+        tms = timed_device(lambda: ops.latent_attention(q, cache, table, o, H, rank, rot, dk ** -0.5, b), flush=flush)
+        if prefill:
+            fl = 2.0 * H * (dk + rank) * pairs
+            put(f"latent_attention_sink_{label}", ms, frac_flops(fl, ms), tms, frac_flops(fl, tms), "bf16 peak", "latent attention")
+        else:
+            by = nseq * keys * dk * 2
+            put(f"latent_attention_sink_{label}", ms, frac_bytes(by, ms), tms, frac_bytes(by, tms), "copy bandwidth", "latent attention")
+        # the latent and the rotated parts on their way into the pages and into the folded queries: half layout beside pairs
+        d = torch.randn(n, dk, device=dev)
+        wn = torch.ones(rank, device=dev)
+        qh = torch.randn(n, H * (dim + rot), device=dev).to(bf)
+        qf = torch.empty(n, H * dk, dtype=bf, device=dev)
+        run = lambda c, s_, half: (ops.latent_store(d, wn, 1e-5, b.pos, b.row_seq, c, s_, table, cache, rank, rot, half_layout=half),
+                                   ops.rotate_heads(qh, H, dim + rot, dim, rot, qf, dk, rank, b.pos, c, s_, half_layout=half))
+        ms = timed_device(lambda: run(cos_h, sin_h, True), flush=flush)
+        tms = timed_device(lambda: run(cos_p, sin_p, False), flush=flush)
+        by = n * (dk * 6 + H * rot * 4)
+        put(f"store_and_rotate_{label}", ms, frac_bytes(by, ms), tms, frac_bytes(by, tms), "copy bandwidth", "the same kernels, pairs (2i, 2i + 1)")
+        # window attention (no cap, no sink, values of their own) beside Favudra's window attention (slopes, values = keys)
+        kc = torch.randn(nseq * blocks + 1, WG, page, hd, device=dev).to(bf)
+        vc = torch.randn(nseq * blocks + 1, WG, page, hd, device=dev).to(bf)
+        wq = torch.randn(n, WH * hd, device=dev).to(bf)
+        wo = torch.empty(n, WH * hd, dtype=bf, device=dev)
+        ms = timed_device(lambda: ops.scored_attention(wq, kc, vc, table, wo, WH, WG, hd, hd, hd ** -0.5, 0.0, False, None, win, b), flush=flush)
+        tms = timed_device(lambda: ops.scored_attention(wq, kc, None, table, wo, WH, WG, hd, hd, hd ** -0.5, 0.0, False, slopes, win, b),
+                           flush=flush)
+        if prefill:
+            fl = 4.0 * WH * hd * wpairs
+            put(f"window_attention_{label}", ms, frac_flops(fl, ms), tms, frac_flops(fl, tms), "bf16 peak", "window attention with slopes")
+        else:
+            by = nseq * min(keys, win) * WG * hd * 2
+            put(f"window_attention_{label}", ms, frac_bytes(2 * by, ms), tms, frac_bytes(by, tms), "copy bandwidth",
+                "window attention with slopes (keys only)")
+        # biases, convolution, unit norm and store beside Favudra's convolution, weighted norm, rotation and store
+        cols = (WH + 2 * WG) * hd
+        u = torch.randn(n, cols, device=dev)
+        cw = torch.randn(cols, taps, device=dev)
+        cwt = cw.t().contiguous()
+        st = torch.zeros(nseq + 1, taps - 1, cols, device=dev)
+        nw = torch.ones(hd, device=dev)
+        bias = torch.randn(cols, device=dev)
+        ms = timed_device(lambda: (ops.qkv_prepare(u, cw, st, nw, nw, 1e-5, None, None, b, table, kc, vc, wq, WH, WG, hd, hd, conv_wt=cwt, bias=bias),
+                                   ops.conv_state_update(u, st, b, taps, b.query_tiles(SEQUENCE_TILE))), flush=flush)
+        tms = timed_device(lambda: (ops.qkv_prepare(u, cw, st, nw, nw, 1e-5, cos_f, sin_f, b, table, kc, vc, wq, WH, WG, hd, hd, conv_wt=cwt),
+                                    ops.conv_state_update(u, st, b, taps, b.query_tiles(SEQUENCE_TILE))), flush=flush)
+        put(f"bias_conv_norm_store_{label}", ms, frac_bytes(n * cols * 6, ms), tms, frac_bytes(n * cols * 6, tms), "copy bandwidth",
+            "convolution, norm, rotation, store")
+        # the layer norm after a sublayer (with the next sublayer's norm) beside the root-mean-square one
+        dd = torch.randn(n, width, device=dev)
+        stream = torch.randn(n, width, device=dev)
+        ww = torch.ones(width, device=dev)
+        a1 = torch.empty(n, width, dtype=bf, device=dev)
+        ms = timed_device(lambda: ops.layernorm_residual(dd, ww, 1e-5, stream, next_weight=ww, next_eps=1e-5, next_out=a1), flush=flush)
+        tms = timed_device(lambda: ops.rmsnorm_residual(dd, ww, 1e-5, stream, next_weight=ww, next_eps=1e-5, next_out=a1), flush=flush)
+        put(f"norm_after_sublayer_{label}", ms, frac_bytes(n * width * 14, ms), tms, frac_bytes(n * width * 14, tms), "copy bandwidth",
+            "root-mean-square norm after a sublayer")
+        # the output gate beside the stand-alone gated step (both read two numbers and write one per output)
+        hv = torch.randn(n, H * vdim, device=dev).to(bf)
+        gl = torch.randn(n, H * vdim, device=dev)
+        gh = torch.randn(n, H, device=dev)
+        gu = torch.randn(n, 2 * H * vdim, device=dev).to(bf)
+        ms = timed_device(lambda: ops.sigmoid_gate(hv, gl, 1), flush=flush)
+        ms_h = timed_device(lambda: ops.sigmoid_gate(hv, gh, vdim), flush=flush)
+        tms = timed_device(lambda: ops.swiglu(gu, hv), flush=flush)
+        put(f"gate_per_entry_{label}", ms, frac_bytes(n * H * vdim * 8, ms), tms, frac_bytes(n * H * vdim * 6, tms), "copy bandwidth",
+            "stand-alone SwiGLU")
+        put(f"gate_per_head_{label}", ms_h, frac_bytes(n * H * vdim * 4, ms_h), tms, frac_bytes(n * H * vdim * 6, tms), "copy bandwidth",
+            "stand-alone SwiGLU")
+        # the gate/up product with the GELU form in its epilogue beside the same product with SiLU
+        x = torch.randn(n, width, device=dev).to(bf)
+        wgu = (torch.randn(2 * ff, width, device=dev) * 0.02).to(bf)
+        hh = torch.empty(n, ff, dtype=bf, device=dev)
+        ms = timed_device(lambda: ops.linear_swiglu(x, wgu, hh, activation="gelu_tanh"), flush=flush)
+        tms = timed_device(lambda: ops.linear_swiglu(x, wgu, hh), flush=flush)
+        if prefill:
+            fl = 2.0 * n * 2 * ff * width
+            put(f"gate_up_gelu_{label}", ms, frac_flops(fl, ms), tms, frac_flops(fl, tms), "bf16 peak", "gate/up product with SiLU")
+        else:
+            by = 2 * ff * width * 2
+            put(f"gate_up_gelu_{label}", ms, frac_bytes(by, ms), tms, frac_bytes(by, tms), "copy bandwidth", "gate/up product with SiLU")
+        # the cap on the logits of the step's wanted rows (no like kernel)
+        rows = 8 if not prefill else 1
+        lg = torch.randn(rows, z["vocab"], device=dev)
+        ms = timed_device(lambda: ops.softcap_rows(lg, 30.0), flush=flush)
+        out[f"logit_cap_{label}"] = {"ms": round(ms, 4), "bound": "latency (one small kernel)"}
+        del cache, kc, vc, wgu
+        torch.cuda.empty_cache()
+    return out
+
+
+def compare_kezuvik(args, pk):
+    import torch
+    from bitwise_b200 import Model
+    z = KEZUVIK_SIZES[args.size]
+    line = {"metric": f"Kezuvik beside Favudra at equal size ({args.size}): prefill of 2,048 tokens and decode at batch "
+                      f"{args.batch}, {args.ctx or 2048:,}-token contexts", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+            "data": "synthetic: random N(0,0.02) weights, prompt ids uniform over the vocabulary", "size": z,
+            "peaks": "of " + pk["source"], "l2": "whole models: weights and cache exceed L2; kernels alone: L2 flushed "
+            "before every repetition"}
+    ctx = args.ctx or 2048
+    for name, cfg in (("kezuvik", kezuvik_config(z)), ("favudra_twin", kezuvik_twin(z))):
+        model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", fast=True)
+        with ClockSampler() as clocks:
+            ms, launches = run_decode(model, args.batch, ctx, args.steps, max(3, args.warmup), args.page)
+        pms = run_prefill(model, 2048, reps=5, warmup=3, page=args.page)
+        line[name] = {"decode_tok_s": round(args.batch / (ms / 1e3), 1), "decode_ms_per_step": round(ms, 4),
+                      "prefill_tok_s": round(2048 / (pms / 1e3), 1), "prefill_ms": round(pms, 3),
+                      "weight_bytes": model.weight_bytes, "gpu_launches": launches, "clocks": clocks.summary()}
+        del model
+        torch.cuda.empty_cache()
+    line["kernels"] = kezuvik_kernel_table(z, pk, args.page)
+    return line
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -898,9 +1107,9 @@ def main():
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="only the headline decode (for profiling runs)")
     ap.add_argument("--skip-prefill", action="store_true")
-    ap.add_argument("--compare", default="", choices=["", "nuderax", "favudra", "sebavik"],
+    ap.add_argument("--compare", default="", choices=["", "nuderax", "favudra", "sebavik", "kezuvik"],
                     help="instead of the headline: this design beside its closest earlier architecture at equal size")
-    ap.add_argument("--size", default="small", choices=sorted(set(NUDERAX_SIZES) | set(FAVUDRA_SIZES) | set(SEBAVIK_SIZES)),
+    ap.add_argument("--size", default="small", choices=sorted(set(NUDERAX_SIZES) | set(FAVUDRA_SIZES) | set(SEBAVIK_SIZES) | set(KEZUVIK_SIZES)),
                     help="layer sizes for --compare")
     args = ap.parse_args()
 
@@ -920,6 +1129,9 @@ def main():
         return 0
     if args.compare == "favudra":
         print(json.dumps(compare_favudra(args, pk)))
+        return 0
+    if args.compare == "kezuvik":
+        print(json.dumps(compare_kezuvik(args, pk)))
         return 0
     if args.compare == "sebavik":
         print(json.dumps(compare_sebavik(args, pk)))

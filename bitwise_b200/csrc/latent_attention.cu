@@ -45,15 +45,27 @@ __device__ __forceinline__ float turned_half(Load load, int i, int pairs, const 
 
 // One block per row: d = the row of the down projection (float32, rank + rot_dim wide).
 // cache[page][slot] = [ d[:rank] / sqrt(mean(d[:rank]^2) + eps) * w | turn(d[rank:]) ].
+// With q_out the q_rank numbers that follow in the row are the queries' latent before its norm:
+// q_out[row] = them / sqrt(mean(them^2) + eps) * q_w, so that one kernel serves both latents of a row
+// where one product formed both.
 __global__ void __launch_bounds__(128)
 latent_store_kernel(const float* __restrict__ d, int d_stride, const float* __restrict__ w, float eps,
                     const int* __restrict__ pos, const int* __restrict__ row_seq, const float* __restrict__ cos_t,
                     const float* __restrict__ sin_t, int pairs, const int* __restrict__ block_table, int max_blocks,
-                    act_t* cache, int rank, int rot_dim, int page, int half_layout) {
+                    act_t* cache, int rank, int rot_dim, int page, int half_layout, const float* __restrict__ q_w,
+                    int q_rank, act_t* q_out) {
   bw::pdl_enter();
   __shared__ float red[32];
   const int r = blockIdx.x;
   const float* dr = d + static_cast<size_t>(r) * d_stride;
+  if (q_out) {
+    const float* qr = dr + rank + rot_dim;
+    float sq = 0.0f;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) sq = __fmaf_rn(qr[i], qr[i], sq);
+    const float qinv = bw::rms_scale(bw::block_sum(sq, red), q_rank, eps);
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+      q_out[static_cast<size_t>(r) * q_rank + i] = bw::from_f<act_t>(bw::rms_apply(qr[i], qinv, q_w[i]));
+  }
   const int p = pos[r];
   const int blk = block_table[static_cast<size_t>(row_seq[r]) * max_blocks + p / page];
   act_t* dst = cache + (static_cast<size_t>(blk) * page + p % page) * (rank + rot_dim);
@@ -602,15 +614,20 @@ constexpr int kQueriesPerWarp = 4;
 BW_API int BW_FN(latent_store)(const float* d, int d_stride, const float* w, float eps, const int* pos,
                                const int* row_seq, const float* cos_t, const float* sin_t, int pairs,
                                const int* block_table, int max_blocks, act_t* cache, int n, int rank, int rot_dim,
-                               int page, int half_layout, cudaStream_t stream) {
+                               int page, int half_layout, const float* q_w, int q_rank, act_t* q_out,
+                               cudaStream_t stream) {
   if (n <= 0) return 0;
   if (half_layout && pairs == 0) half_layout = 0;
+  if (q_out && (!q_w || q_rank <= 0)) {
+    bw::set_error("latent_store: the queries' latent needs a weight and a size");
+    return -1;
+  }
   if (rank <= 0 || rot_dim < 0 || 2 * pairs > rot_dim || (pairs > 0 && !cos_t)) {
     bw::set_error("latent_store: rank %d, rotated part %d, %d pairs", rank, rot_dim, pairs);
     return -1;
   }
   bw::launch_pdl(latent_store_kernel, dim3(n), dim3(128), 0, stream, d, d_stride, w, eps, pos, row_seq, cos_t, sin_t,
-                 pairs, block_table, max_blocks, cache, rank, rot_dim, page, half_layout);
+                 pairs, block_table, max_blocks, cache, rank, rot_dim, page, half_layout, q_w, q_rank, q_out);
   return bw::launch_status();
 }
 

@@ -30,6 +30,7 @@ constexpr int kPrepWarps = 4;
 struct PrepArgs {
   const float* u;            // [n, cols] projected rows: q heads, then k heads, then v heads
   int cols;
+  int u_stride;              // floats between two rows of u (cols, or more where the rows are columns of a wider product)
   const float* bias;         // [cols] added to every projected row (also to rows read from the state), or null
   const float* vmix_src;     // [n, v_heads * vdim] values that this layer's values are mixed with, or null
   const float* vmix_lambda;  // one number: v <- (1 - lambda) v + lambda vmix_src
@@ -93,13 +94,13 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qkv_prepare_kernel(const Prep
             if (p - back < 0) continue;
             const int rr = r - back;
             float src = rr >= row0
-                            ? a.u[static_cast<size_t>(rr) * a.cols + c]
+                            ? a.u[static_cast<size_t>(rr) * a.u_stride + c]
                             : a.conv_state[(static_cast<size_t>(slot) * (a.taps - 1) + (a.taps - 1 - (row0 - rr))) * a.cols + c];
             if (a.bias) src = __fadd_rn(src, a.bias[c]);
             v = __fmaf_rn(a.conv_w[static_cast<size_t>(c) * a.taps + t], src, v);
           }
         } else {
-          v = a.u[static_cast<size_t>(r) * a.cols + c];
+          v = a.u[static_cast<size_t>(r) * a.u_stride + c];
           if (a.bias) v = __fadd_rn(v, a.bias[c]);
         }
         if (!turns && (a.vmix_src || a.v_keep)) {  // a value head (keys and queries turn or are normed; values neither)
@@ -176,7 +177,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qkv_prepare_vec_kernel(const 
   const int row0 = a.seq_row0[seq];
   const int slot = a.conv_state ? a.seq_slot[seq] : 0;
   const int total = a.heads + a.kv_heads + a.v_heads;
-  const float* urow = a.u + static_cast<size_t>(r) * a.cols;
+  const float* urow = a.u + static_cast<size_t>(r) * a.u_stride;
   for (int hs = blockIdx.y * kPrepWarps + warp; hs < total; hs += kPrepWarps * gridDim.y) {
     int size, col0;
     const float* norm_w;
@@ -200,7 +201,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qkv_prepare_vec_kernel(const 
             const int back = a.taps - 1 - t;
             if (p - back < 0) continue;
             const int rr = r - back;
-            const float* src = rr >= row0 ? urow - static_cast<size_t>(back) * a.cols + c
+            const float* src = rr >= row0 ? urow - static_cast<size_t>(back) * a.u_stride + c
                                           : a.conv_state + (static_cast<size_t>(slot) * (a.taps - 1) + (a.taps - 1 - (row0 - rr))) * a.cols + c;
             float4 x = *reinterpret_cast<const float4*>(src);
             if (a.bias) {
@@ -286,7 +287,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qkv_prepare_vec_kernel(const 
 constexpr int kMaxTaps = 16;
 
 __global__ void __launch_bounds__(128)
-conv_state_update_kernel(const float* __restrict__ u, int cols, float* state, int taps, const int* __restrict__ tile_seq,
+conv_state_update_kernel(const float* __restrict__ u, int u_stride, int cols, float* state, int taps, const int* __restrict__ tile_seq,
                          const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                          const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot) {
   bw::pdl_enter();
@@ -303,7 +304,7 @@ conv_state_update_kernel(const float* __restrict__ u, int cols, float* state, in
     const int p = pos0 + cnt - (taps - 1) + i;
     float v = 0.0f;
     if (p >= pos0)
-      v = u[static_cast<size_t>(row0 + p - pos0) * cols + c];
+      v = u[static_cast<size_t>(row0 + p - pos0) * u_stride + c];
     else if (p >= 0)
       v = st[static_cast<size_t>(p - pos0 + taps - 1) * cols];
     keep[i] = v;
@@ -855,8 +856,12 @@ BW_API int BW_FN(qkv_prepare)(const float* u, int cols, const float* conv_w, con
                               const int* seq_slot, const int* block_table, int max_blocks, void* kcache, void* vcache,
                               void* q_out, int n, int heads, int kv_heads, int dim, int vdim, int page,
                               const float* bias, const float* vmix_src, const float* vmix_lambda, float* v_keep,
-                              cudaStream_t stream) {
+                              int u_stride, cudaStream_t stream) {
   if (n <= 0) return 0;
+  if (u_stride < cols) {
+    bw::set_error("qkv_prepare: rows %d floats apart do not hold %d columns", u_stride, cols);
+    return -1;
+  }
   if (dim > kMaxE * 32 || vdim > kMaxE * 32) {
     bw::set_error("qkv_prepare: head sizes %d / %d (up to %d)", dim, vdim, kMaxE * 32);
     return -1;
@@ -867,7 +872,7 @@ BW_API int BW_FN(qkv_prepare)(const float* u, int cols, const float* conv_w, con
   }
   PrepArgs a;
   a.bias = bias, a.vmix_src = vmix_src, a.vmix_lambda = vmix_lambda, a.v_keep = v_keep;
-  a.u = u, a.cols = cols, a.conv_w = conv_w, a.conv_wt = conv_w ? conv_wt : nullptr, a.taps = taps;
+  a.u = u, a.cols = cols, a.u_stride = u_stride, a.conv_w = conv_w, a.conv_wt = conv_w ? conv_wt : nullptr, a.taps = taps;
   a.conv_state = taps > 1 ? conv_state : nullptr;
   a.q_norm = q_norm, a.k_norm = k_norm, a.eps = eps, a.cos_t = cos_t, a.sin_t = sin_t, a.pairs = cos_t ? pairs : 0;
   a.pos = pos, a.row_seq = row_seq, a.seq_row0 = seq_row0, a.seq_pos0 = seq_pos0, a.seq_slot = seq_slot;
@@ -876,7 +881,7 @@ BW_API int BW_FN(qkv_prepare)(const float* u, int cols, const float* conv_w, con
   a.heads = heads, a.kv_heads = kv_heads, a.v_heads = vcache ? kv_heads : 0, a.dim = dim, a.vdim = vdim, a.page = page;
   const int total = heads + kv_heads + a.v_heads;
   // four entries per lane where every head and row starts on 16 bytes (and the taps came transposed)
-  const bool by_four = dim % 4 == 0 && vdim % 4 == 0 && cols % 4 == 0 && (!conv_w || conv_wt) &&
+  const bool by_four = dim % 4 == 0 && vdim % 4 == 0 && cols % 4 == 0 && u_stride % 4 == 0 && (!conv_w || conv_wt) &&
                        ((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(conv_state) |
                          reinterpret_cast<uintptr_t>(conv_wt) | reinterpret_cast<uintptr_t>(q_norm) |
                          reinterpret_cast<uintptr_t>(k_norm) | reinterpret_cast<uintptr_t>(bias) |
@@ -888,15 +893,20 @@ BW_API int BW_FN(qkv_prepare)(const float* u, int cols, const float* conv_w, con
   return bw::launch_status();
 }
 
+// u_stride: floats between two rows of u (at least cols).
 BW_API int BW_FN(conv_state_update)(const float* u, int cols, float* state, int taps, const int* tile_seq,
                                     const int* tile_row0, const int* tile_rows, int tiles, const int* seq_pos0,
-                                    const int* seq_slot, cudaStream_t stream) {
+                                    const int* seq_slot, int u_stride, cudaStream_t stream) {
   if (tiles <= 0 || taps <= 1) return 0;
+  if (u_stride < cols) {
+    bw::set_error("conv_state_update: rows %d floats apart do not hold %d columns", u_stride, cols);
+    return -1;
+  }
   if (taps - 1 > kMaxTaps) {
     bw::set_error("conv_state_update: %d taps (up to %d)", taps, kMaxTaps + 1);
     return -1;
   }
-  bw::launch_pdl(conv_state_update_kernel, dim3(tiles, (cols + 127) / 128), dim3(128), 0, stream, u, cols, state, taps,
+  bw::launch_pdl(conv_state_update_kernel, dim3(tiles, (cols + 127) / 128), dim3(128), 0, stream, u, u_stride, cols, state, taps,
                  tile_seq, tile_row0, tile_rows, seq_pos0, seq_slot);
   return bw::launch_status();
 }

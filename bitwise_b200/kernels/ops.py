@@ -677,11 +677,13 @@ class KernelOps:
 
     def latent_store(self, d: torch.Tensor, weight: torch.Tensor, eps: float, pos: torch.Tensor, row_seq: torch.Tensor,
                      cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], block_table: torch.Tensor,
-                     cache: torch.Tensor, rank: int, rot_dim: int, half_layout: bool = False) -> None:
+                     cache: torch.Tensor, rank: int, rot_dim: int, half_layout: bool = False, q_latent=None) -> None:
         """For every row of ``d`` (float32 [n, >= rank + rot_dim], the row's first columns are used): the
         first ``rank`` entries divided by their root mean square (eps inside the root) times ``weight``, the
         next ``rot_dim`` turned pair by pair (2i with 2i+1; ``half_layout``: i with i + pairs) by row ``pos``
-        of the tables, both stored at the row's place in ``cache`` [pages, page, rank + rot_dim]."""
+        of the tables, both stored at the row's place in ``cache`` [pages, page, rank + rot_dim].  With
+        ``q_latent`` = (weight [q_rank], out act_dtype [n, q_rank]) the ``q_rank`` columns that follow in the
+        same rows are normed as well, with that weight, into ``out``: the queries' latent, in the same kernel."""
         n = d.shape[0]
         _need_rows(d, torch.float32, "latent_store d")
         _need(weight, torch.float32, "latent_store weight", 1)
@@ -692,9 +694,19 @@ class KernelOps:
         if d.shape[1] < rank + rot_dim or cache.shape[2] != rank + rot_dim or weight.shape[0] != rank:
             raise KernelError("latent_store: widths do not fit rank + rot_dim")
         pairs = self._check_tables(cos, sin, rot_dim, "latent_store")
+        q_w = q_out = None
+        q_rank = 0
+        if q_latent is not None:
+            q_w, q_out = q_latent
+            q_rank = q_w.shape[0]
+            _need(q_w, torch.float32, "latent_store q weight", 1)
+            _need(q_out, self.act_dtype, "latent_store q out", 2)
+            if d.shape[1] < rank + rot_dim + q_rank or tuple(q_out.shape) != (n, q_rank):
+                raise KernelError("latent_store: the queries' latent does not fit the rows")
         self._pcall("latent_store", _p(d), _c_int(d.stride(0)), _p(weight), _c_float(eps), _p(pos), _p(row_seq), _p(cos),
                     _p(sin), _c_int(pairs), _p(block_table), _c_int(block_table.shape[1]), _p(cache), _c_int(n),
-                    _c_int(rank), _c_int(rot_dim), _c_int(cache.shape[1]), _c_int(int(bool(half_layout))), self._stream())
+                    _c_int(rank), _c_int(rot_dim), _c_int(cache.shape[1]), _c_int(int(bool(half_layout))), _p(q_w),
+                    _c_int(q_rank), _p(q_out), self._stream())
 
     @staticmethod
     def _check_tables(cos, sin, rot_dim: int, what: str) -> int:
@@ -1087,7 +1099,7 @@ class KernelOps:
         kv_heads * vdim]) and ``vmix_lambda`` (one float32): the values become (1 - lambda) v + lambda vmix_src
         before they are stored; ``v_keep`` (same shape) receives the values as stored, in float32."""
         n, cols = u.shape
-        _need(u, torch.float32, "qkv_prepare u", 2)
+        _need_rows(u, torch.float32, "qkv_prepare u")
         _need(q_out, self.act_dtype, "qkv_prepare q_out", 2)
         _need(block_table, torch.int32, "qkv_prepare block_table", 2)
         _need(kcache, self.act_dtype, "qkv_prepare kcache", 4)
@@ -1138,19 +1150,19 @@ class KernelOps:
                     _p(batch.seq_pos0), _p(batch.seq_slot), _p(block_table), _c_int(block_table.shape[1]), _p(kcache),
                     _p(vcache if write_kv_heads else None), _p(q_out), _c_int(n), _c_int(heads), _c_int(write_kv_heads),
                     _c_int(dim), _c_int(vdim), _c_int(kcache.shape[2]), _p(bias), _p(vmix_src), _p(vmix_lambda), _p(v_keep),
-                    self._stream())
+                    _c_int(u.stride(0)), self._stream())
 
     def conv_state_update(self, u: torch.Tensor, state: torch.Tensor, batch, taps: int, seq_tiles) -> None:
         """state[slot of s][i] = the projected row of position end_s - (taps - 1) + i for every sequence s
         of the step (``seq_tiles``: one tile per sequence), end_s its length after the step: from the
         step's rows ``u``, from the old state, or zero before position 0."""
-        _need(u, torch.float32, "conv_state_update u", 2)
+        _need_rows(u, torch.float32, "conv_state_update u")
         _need(state, torch.float32, "conv_state_update state", 3)
         t_seq, t_row0, t_rows, t_count = seq_tiles
         if tuple(state.shape[1:]) != (taps - 1, u.shape[1]):
             raise KernelError("conv_state_update: the state is not [slots, taps - 1, cols]")
         self._mcall("conv_state_update", _p(u), _c_int(u.shape[1]), _p(state), _c_int(taps), _p(t_seq), _p(t_row0),
-                    _p(t_rows), _c_int(t_count), _p(batch.seq_pos0), _p(batch.seq_slot), self._stream())
+                    _p(t_rows), _c_int(t_count), _p(batch.seq_pos0), _p(batch.seq_slot), _c_int(u.stride(0)), self._stream())
 
     def scored_attention(self, q: torch.Tensor, kcache: torch.Tensor, vcache: Optional[torch.Tensor],
                          block_table: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,

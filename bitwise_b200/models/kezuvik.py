@@ -58,7 +58,7 @@ def build_kezuvik(config: KezuvikConfig) -> DecoderModel:
             second = m.kind == "latent_attention_2"
             mixer = LatentAttention(c.width, m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.scale, c.eps,
                                     position=rotaries[key], q_rank=m.q_rank, sink=second,
-                                    gate="head" if second else "entry")
+                                    gate="head" if second else "entry", stack_inputs=True)
         else:
             mixer = ScoredAttention(c.width, m.heads, m.kv_heads, m.dim, m.vdim, m.scale, c.eps, conv_taps=m.conv or 0,
                                     qk_norm="unit", window=m.window, bias=True, gate="entry")

@@ -44,7 +44,7 @@ class LatentAttention(Mixer):
     def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, rank: int, scale: float, eps: float,
                  position: Optional[PositionEncoding] = None, q_rank: Optional[int] = None,
                  shares_cache: bool = False, window: Optional[int] = None, names: Optional[Dict[str, str]] = None,
-                 sink: bool = False, gate: Optional[str] = None):
+                 sink: bool = False, gate: Optional[str] = None, stack_inputs: bool = False):
         for what, v in (("heads", heads), ("dim", dim), ("vdim", vdim), ("rank", rank)):
             if v <= 0:
                 raise ValueError(f"latent attention: {what} must be positive, got {v}")
@@ -60,6 +60,10 @@ class LatentAttention(Mixer):
         self.sink, self.sinks = bool(sink), None
         self.gate = OutputGate(width, heads, vdim, gate, self.names["gate"]) if gate else None
         self.half_layout = getattr(position, "layout", "pairs") == "half"
+        # one product for everything that reads the mixer's input (both down projections and the gate), its rows
+        # laid out [keys' and values' latent | rotated key part | queries' latent | gate]
+        self.stacked = bool(stack_inputs) and q_rank is not None and not shares_cache
+        self.w_in = None
 
     @property
     def _layout(self):
@@ -115,6 +119,14 @@ class LatentAttention(Mixer):
             self.sinks = state[f"{prefix}.{n['sink']}"]
         if self.gate is not None:
             self.gate.load_params(state, prefix)
+        if self.stacked:
+            parts = [self.w_kv_down, self.w_q_down] + ([self.gate.weight] if self.gate is not None else [])
+            self.w_in = torch.cat(parts, 0).contiguous()
+            # the separate matrices become views of the stacked one (a run that only reads a cache uses them)
+            dk = self.rank + self.rot_dim
+            self.w_kv_down, self.w_q_down = self.w_in[:dk], self.w_in[dk:dk + self.q_rank]
+            if self.gate is not None:
+                self.gate.weight = self.w_in[dk + self.q_rank:]
 
     def param_bytes(self) -> int:
         ts = (self.w_q, self.w_q_down, self.q_norm, self.w_kv_down, self.kv_norm, self.w_k_fold, self.w_v_up, self.w_o,
@@ -131,7 +143,17 @@ class LatentAttention(Mixer):
         tables = self.position.rotary_tables(x.device) if self.position is not None and self.rot_dim else None
         cos, sin = tables if tables is not None else (None, None)
         # queries
-        if self.q_rank is None:
+        gate_logits = None
+        stacked = self.stacked and cache.writable
+        if stacked:
+            u = ws.rows("latent_in32", n, self.w_in.shape[0], torch.float32)
+            ops.linear(xn, self.w_in, u)
+            q_in = ws.rows("latent_q", n, self.q_rank, act)
+            ops.latent_store(u, self.kv_norm, self.eps, ctx.pos, ctx.row_seq, cos, sin, cache.block_table, cache.latent,
+                             self.rank, self.rot_dim, q_latent=(self.q_norm, q_in), **self._layout)
+            if self.gate is not None:
+                gate_logits = u[:, dk + self.q_rank:]
+        elif self.q_rank is None:
             q_in = xn
         else:
             cq = ws.rows("latent_q32", n, self.q_rank, torch.float32)
@@ -141,7 +163,7 @@ class LatentAttention(Mixer):
         q = ws.rows("latent_heads_q", n, self.q_width, act)
         ops.linear(q_in, self.w_q, q)
         # this layer's entry of the cache
-        if cache.writable and not self.shares_cache:
+        if cache.writable and not self.shares_cache and not stacked:
             d = ws.rows("latent_kv32", n, dk, torch.float32)
             ops.linear(xn, self.w_kv_down, d)
             ops.latent_store(d, self.kv_norm, self.eps, ctx.pos, ctx.row_seq, cos, sin, cache.block_table, cache.latent,
@@ -158,7 +180,7 @@ class LatentAttention(Mixer):
         values = ws.rows("latent_values", n, self.heads * self.vdim, act)
         ops.grouped_linear(mixed, self.w_v_up, values, n, x_group_cols=self.rank, o_group_cols=self.vdim)
         if self.gate is not None:
-            self.gate.apply(ctx, xn, values)
+            self.gate.apply(ctx, xn, values, gate_logits)
         ops.linear(values, self.w_o, x, residual=x if accumulate else None)
 
 

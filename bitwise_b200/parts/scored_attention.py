@@ -163,7 +163,10 @@ class ScoredAttention(Mixer):
             self.q_norm = state[f"{prefix}.{n['q']}{n['norm']}"]
             self.k_norm = None if self.shares_cache else state[f"{prefix}.{n['k']}{n['norm']}"]
         if self.gate is not None:
+            # the gate reads the mixer's input like the projections: its rows ride behind theirs in one product
             self.gate.load_params(state, prefix)
+            self.w_in = torch.cat([self.w_in, self.gate.weight], 0).contiguous()
+            self.gate.weight = self.w_in[self.cols:]
         self.w_o = state[f"{prefix}.{n['out']}"]
         if self.bias:
             self.b_in = torch.cat([state[f"{prefix}.{name}{n['bias']}"] for name, _, _, _ in proj], 0).contiguous()
@@ -180,16 +183,21 @@ class ScoredAttention(Mixer):
         ts = (self.w_in, self.w_o, self.conv_w, None if self.unit_norm else self.q_norm,
               None if self.unit_norm else self.k_norm, self.b_in, self.vmix, self.dist_a, self.dist_b,
               self.sinks)  # (the transposed taps are a copy)
-        return sum(t.numel() * t.element_size() for t in ts if t is not None) + (
-            self.gate.param_bytes() if self.gate is not None else 0)
+        return sum(t.numel() * t.element_size() for t in ts if t is not None)  # (the gate's rows are part of w_in)
 
     # -- one step --------------------------------------------------------------------------
     def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, cache: PagedKVView,
                 accumulate: bool = True) -> None:
         """``accumulate`` False: the output is written to ``x`` instead of added to it."""
         ops, ws, n = ctx.ops, ctx.workspace, ctx.n
-        u = ws.rows("scored_qkv32", n, self.cols, torch.float32)
-        ops.linear(xn, self.w_in, u)
+        gate_logits = None
+        if self.gate is not None:
+            wide = ws.rows("scored_qkv32", n, self.cols + self.gate.cols, torch.float32)
+            ops.linear(xn, self.w_in, wide)
+            u, gate_logits = wide[:, :self.cols], wide[:, self.cols:]
+        else:
+            u = ws.rows("scored_qkv32", n, self.cols, torch.float32)
+            ops.linear(xn, self.w_in, u)
         tables = self.position.rotary_tables(x.device) if self.position is not None and self.rot_dims else None
         cos, sin = tables if tables is not None else (None, None)
         q = ws.rows("scored_q", n, self.q_cols, ctx.act_dtype)
@@ -215,7 +223,7 @@ class ScoredAttention(Mixer):
                              self.scale, self.softcap or 0.0, self.sink, self.slopes, self.window or 0, ctx,
                              dist_a=self.dist_a, dist_b=self.dist_b, sinks=self.sinks, keep_first=self.keep_first)
         if self.gate is not None:
-            self.gate.apply(ctx, xn, mixed)
+            self.gate.apply(ctx, xn, mixed, gate_logits)
         ops.linear(mixed, self.w_o, x, residual=x if accumulate else None)
 
 

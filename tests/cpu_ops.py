@@ -292,8 +292,13 @@ class CpuOps:
             out[..., 0:2 * pairs:2], out[..., 1:2 * pairs:2] = a * c - b * s, b * c + a * s
         return out
 
-    def latent_store(self, d, weight, eps, pos, row_seq, cos, sin, block_table, cache, rank, rot_dim, half_layout=False):
+    def latent_store(self, d, weight, eps, pos, row_seq, cos, sin, block_table, cache, rank, rot_dim, half_layout=False,
+                     q_latent=None):
         page = cache.shape[1]
+        if q_latent is not None:
+            q_w, q_out = q_latent
+            cq = d[:, rank + rot_dim:rank + rot_dim + q_w.shape[0]]
+            q_out.copy_((cq * torch.rsqrt(cq.pow(2).mean(-1, keepdim=True) + eps) * q_w).to(q_out.dtype))
         p = pos.long()
         c = d[:, :rank]
         c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * weight

@@ -119,6 +119,13 @@ def test_half_layout_rotation_into_the_pages_and_on_the_queries(dtype, rot_dim, 
     w = (1.0 + 0.2 * torch.randn(rank, generator=g)).to(DEV)
     cache = torch.zeros(int(table.max()) + 1, page, rank + rot_dim, dtype=act(dtype), device=DEV)
     ops.latent_store(d, w, 1e-5, b.pos, b.row_seq, cos, sin, table, cache, rank, rot_dim, half_layout=True)
+    # the same with the queries' latent taken from the columns behind, normed in the same kernel
+    again = torch.zeros_like(cache)
+    qw = (1.0 + 0.2 * torch.randn(7, generator=g)).to(DEV)
+    q_lat = torch.zeros(b.n, 7, dtype=act(dtype), device=DEV)
+    ops.latent_store(wide, w, 1e-5, b.pos, b.row_seq, cos, sin, table, again, rank, rot_dim, half_layout=True, q_latent=(qw, q_lat))
+    assert torch.equal(again, cache)
+    close(q_lat, P.unit_rms(wide[:, rank + rot_dim:].to(F64).cpu(), 1e-5) * qw.to(F64).cpu(), dtype, "the queries' latent")
     d64 = d.to(F64).cpu()
     want = torch.cat([P.unit_rms(d64[:, :rank], 1e-5) * w.to(F64).cpu(), P.rotate_half(d64[:, rank:], b.positions, rot)], 1)
     rows = [cache[int(table[int(b.row_seq[r]), p // page]), p % page] for r, p in enumerate(b.positions)]

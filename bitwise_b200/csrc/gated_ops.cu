@@ -37,13 +37,13 @@ __global__ void sigmoid_gate_kernel(act_t* v, int cols, const float* __restrict_
 }
 
 // The same for rows whose length is a multiple of 8, with groups of one entry or of a multiple of 8: a thread takes
-// 8 neighbouring entries (16 or 32 bytes at a time) of the row blockIdx.y.
+// 8 neighbouring entries (16 or 32 bytes at a time) of the row blockIdx.x.
 __global__ void __launch_bounds__(256)
 sigmoid_gate_vec_kernel(act_t* v, int cols, const float* __restrict__ g, int g_stride, int group) {
   bw::pdl_enter();
-  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (c >= cols) return;
-  const size_t r = blockIdx.y;
+  const size_t r = blockIdx.x;
   act_t* at = v + r * cols + c;
   float s[8];
   if (group == 1) {
@@ -108,9 +108,9 @@ BW_API int BW_FN(sigmoid_gate)(void* v, int n, int cols, const float* g, int g_s
   }
   const bool aligned = reinterpret_cast<uintptr_t>(v) % 32 == 0 &&
                        (group > 1 || (reinterpret_cast<uintptr_t>(g) % 16 == 0 && g_stride % 4 == 0));
-  if (cols % 8 == 0 && (group == 1 || group % 8 == 0) && aligned && n <= 65535) {
+  if (cols % 8 == 0 && (group == 1 || group % 8 == 0) && aligned) {
     const int threads = cols / 8 >= 256 ? 256 : (cols / 8 + 31) / 32 * 32;
-    bw::launch_pdl(sigmoid_gate_vec_kernel, dim3((cols / 8 + threads - 1) / threads, n), dim3(threads), 0, stream, static_cast<act_t*>(v), cols, g,
+    bw::launch_pdl(sigmoid_gate_vec_kernel, dim3(n, (cols / 8 + threads - 1) / threads), dim3(threads), 0, stream, static_cast<act_t*>(v), cols, g,
                    g_stride, group);
     return bw::launch_status();
   }
